@@ -1,0 +1,124 @@
+/*
+ * nvfp4_b200.h -- C ABI of the B200 (sm_100a) NVFP4 quantize + block-scaled
+ * FP4 GEMM library (libnvfp4_b200.so).
+ *
+ * Every entry point takes raw device pointers, sizes and a CUDA stream
+ * (passed as void*, i.e. a cudaStream_t), launches asynchronously on that
+ * stream, never synchronises with the host, never allocates, and returns an
+ * nvfp4_status.  Nothing falls back to the CPU: on a device that is not
+ * compute capability 10.x the calls return NVFP4_ERR_UNSUPPORTED_ARCH.
+ *
+ * Packed-tensor layout (identical to the reference's):
+ *   data    uint8 [rows, cols/2]   two E2M1 codes per byte, even element in
+ *                                  the low nibble
+ *   scales  uint8 [rows, cols/16]  FP8-E4M3 bits, one per 16-element K-block,
+ *                                  linear row-major
+ *   global  float                  the FP32 per-tensor scale amax/(6*448)
+ * The GEMM additionally reads scales in the tensor-core layout ("swizzled":
+ * 512-byte atoms of 128 rows x 4 K-blocks ordered [32][4][4], rows padded to
+ * 256 and K-blocks to 16); quantize emits it directly, and
+ * nvfp4_swizzle_scales converts a linear buffer.
+ *
+ * Reference interfaces are cited by path inside the reference project.
+ */
+#ifndef NVFP4_B200_H_
+#define NVFP4_B200_H_
+
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define NVFP4_API __attribute__((visibility("default")))
+#else
+#define NVFP4_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum nvfp4_status {
+  NVFP4_OK = 0,
+  NVFP4_ERR_BAD_ARG = 1,          /* null pointer, negative size, cols % 16 != 0 ... */
+  NVFP4_ERR_BAD_ALIGN = 2,        /* pointer or leading dimension not 16-byte aligned */
+  NVFP4_ERR_UNSUPPORTED_ARCH = 3, /* current device is not sm_100 */
+  NVFP4_ERR_LAUNCH_FAILED = 4,    /* cudaGetLastError() after the launch */
+  NVFP4_ERR_TIMEOUT = 5           /* a device-side bounded wait gave up */
+} nvfp4_status;
+
+/* Epilogue activation selector of nvfp4_gemm. */
+#define NVFP4_ACT_NONE 0
+#define NVFP4_ACT_GELU_TANH 1
+
+/* Human-readable name of a status code (static storage). */
+NVFP4_API const char* nvfp4_status_string(int status);
+
+/* Library version, major*10000 + minor*100 + patch. */
+NVFP4_API int nvfp4_version(void);
+
+/* Replaces the module-level init() of fx/src/s4/nvfp4/bindings.cpp:16-31,
+ * which refuses compute capability < 12: here the requirement is exactly
+ * 10.x.  Writes major/minor when the pointers are non-null. */
+NVFP4_API int nvfp4_init(int device, int* cc_major, int* cc_minor);
+
+/* Per-tensor max|x| into a device fp32 slot (zeroed by this call, on the
+ * stream).  Replaces the host-synchronising input.abs().max().item() of
+ * fx/src/s4/nvfp4/tensor.cpp:54 and linear/nvfp4_linear.cpp:79. */
+NVFP4_API int nvfp4_amax_bf16(const void* x_bf16, int64_t n, float* amax_dev, void* stream);
+
+/* Bytes of the swizzled scale buffer for a [rows, cols] tensor. */
+NVFP4_API int64_t nvfp4_swizzled_scale_bytes(int64_t rows, int64_t cols);
+
+/* bf16 [rows, cols] -> packed E2M1 + E4M3 block scales + FP32 tensor scale,
+ * the tensor amax being read from a device slot (no host sync).  Replaces
+ * launch_block_1d_quantization_cuda_te (fx/src/s4/nvfp4/quantization.cuh:
+ * 52-54) with its global_amax argument moved to device memory.
+ *   scales_linear   may be null (skip the linear copy)
+ *   scales_swizzled may be null (skip the tensor-core copy)
+ *   global_scale_dev may be null; otherwise receives amax/(6*448) as 1/S_enc */
+NVFP4_API int nvfp4_quantize_bf16(const void* x_bf16, int64_t rows, int64_t cols, const float* amax_dev,
+                        uint8_t* packed, uint8_t* scales_linear, uint8_t* scales_swizzled,
+                        float* global_scale_dev, void* stream);
+
+/* Same arithmetic with the reference launcher's exact argument list: flat
+ * element count and global_amax by value.  Replaces
+ * launch_block_1d_quantization_cuda_te (fx/src/s4/nvfp4/quantization.cuh:52-54).
+ * n must be a multiple of 16. */
+NVFP4_API int nvfp4_quantize_bf16_amax(const void* x_bf16, uint8_t* packed, uint8_t* scales, int64_t n,
+                             float global_amax, void* stream);
+
+/* packed + linear scales -> bf16, the tensor amax read from the device slot
+ * nvfp4_amax_bf16 filled.  Replaces launch_block_1d_dequantization_cuda_te
+ * (fx/src/s4/nvfp4/quantization.cuh:56-58). */
+NVFP4_API int nvfp4_dequantize_bf16(const uint8_t* packed, const uint8_t* scales_linear, int64_t rows,
+                          int64_t cols, const float* amax_dev, void* out_bf16, void* stream);
+
+/* Same with global_amax by value, the reference launcher's argument list
+ * (fx/src/s4/nvfp4/quantization.cuh:56-58). */
+NVFP4_API int nvfp4_dequantize_bf16_amax(const uint8_t* packed, const uint8_t* scales, void* out_bf16,
+                               int64_t n, float global_amax, void* stream);
+
+/* Linear [rows, cols/16] scales -> swizzled layout (pad bytes zeroed).
+ * Reconciles fx/src/s4/nvfp4/tensor.cpp:15 (linear scales) with the layout
+ * fx/src/s4/nvfp4/kernel.cu:91-96 expects. */
+NVFP4_API int nvfp4_swizzle_scales(const uint8_t* scales_linear, int64_t rows, int64_t cols,
+                         uint8_t* scales_swizzled, void* stream);
+
+/* Block-scaled FP4 GEMM on the tcgen05 tensor cores:
+ *   D[M,N] (bf16) = beta * C + gate[n] * act( alpha * ga * gb * sum_k a*sfa * b*sfb + bias[n] )
+ * A is [M, K/2] packed, B is [N, K/2] packed (both K-contiguous), scales are
+ * swizzled, ga/gb are the device FP32 tensor scales (null = 1).  bias (bf16
+ * [N]), gate (fp32 [N]) and C (bf16 [M,N]) may be null.  Replaces
+ * blackwell_fp4_gemm_prequantized (fx/src/s4/nvfp4/kernel.cuh:13-18,
+ * kernel.cu:15-159) without its M,N,K % 128 restriction: any M >= 1,
+ * N % 8 == 0, K % 32 == 0.  status_dev (nullable) is a device int the kernel
+ * sets non-zero if a bounded wait expires. */
+NVFP4_API int nvfp4_gemm(const uint8_t* a_packed, const uint8_t* b_packed, const uint8_t* a_scales_swizzled,
+               const uint8_t* b_scales_swizzled, const float* a_global_scale_dev,
+               const float* b_global_scale_dev, int64_t M, int64_t N, int64_t K, float alpha,
+               float beta, const void* c_bf16, const void* bias_bf16, const float* gate_f32,
+               int act, void* d_bf16, int* status_dev, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NVFP4_B200_H_ */

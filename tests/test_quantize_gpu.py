@@ -1,0 +1,212 @@
+"""GPU parity of the quantizer family, through the C ABI, against the CPU
+oracle: packed nibbles, E4M3 scales and the FP32 tensor scale are bit-exact."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import bits_of, from_bits, outlier_weight_bf16, randn_bf16, student_t_bf16
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "nvfp4_cases.npz")
+
+
+@pytest.fixture(scope="module")
+def nv():
+    from blackwell_diffusion_rtx6000_5090_i2v_b200 import nvfp4
+    return nvfp4
+
+
+def _check_against_oracle(nv, oracle, x_cpu: torch.Tensor):
+    t = nv.FP4Tensor.from_bfloat16(x_cpu.cuda())
+    xb = bits_of(x_cpu).reshape(-1, x_cpu.shape[-1])
+    packed, scales, amax = oracle.quantize(xb)
+    assert float(t.global_amax().item()) == amax
+    assert np.float32(t.global_scale().item()) == np.float32(oracle.global_decode_scale(amax))
+    assert np.array_equal(t.quantized_data().cpu().numpy(), packed.reshape(-1))
+    assert np.array_equal(t.scale_factors().cpu().numpy(), scales.reshape(-1))
+    swz = oracle.swizzle_scales(scales, xb.shape[1])
+    assert np.array_equal(t.scale_factors_swizzled().cpu().numpy(), swz)
+    deq = t.to_bfloat16()
+    assert np.array_equal(bits_of(deq).reshape(xb.shape), oracle.dequantize_bf16(packed, scales, amax))
+    return t
+
+
+@pytest.mark.parametrize("shape,seed", [((128, 128), 0), ((256, 272), 1), ((304, 304), 2),
+                                        ((1, 16), 3), ((17, 48), 4), ((129, 3072), 5),
+                                        ((1000, 1024), 6)])
+def test_normal_inputs_bit_exact(nv, oracle, shape, seed):
+    _check_against_oracle(nv, oracle, randn_bf16(shape, seed))
+
+
+def test_heavy_tails_and_outliers_bit_exact(nv, oracle):
+    _check_against_oracle(nv, oracle, student_t_bf16((333, 512), 10))
+    _check_against_oracle(nv, oracle, outlier_weight_bf16((256, 1024), 11))
+
+
+def test_every_bf16_value_bit_exact(nv, oracle):
+    # all 65536 bit patterns except NaN/Inf, shuffled into blocks, at several magnitudes
+    allb = np.arange(65536, dtype=np.uint16)
+    finite = allb[(allb & 0x7F80) != 0x7F80]
+    rng = np.random.default_rng(5)
+    for rep in range(3):
+        v = rng.permutation(finite)
+        v = v[: v.size // 16 * 16].reshape(-1, 16)
+        _check_against_oracle(nv, oracle, from_bits(v))
+    # same codes but confined to a narrow range so that the encode scale is moderate
+    small = finite[((finite & 0x7F80) >= (120 << 7)) & ((finite & 0x7F80) <= (132 << 7))]
+    v = rng.permutation(small)
+    v = v[: v.size // 64 * 64].reshape(-1, 64)
+    _check_against_oracle(nv, oracle, from_bits(v))
+
+
+def test_golden_vectors(nv, oracle):
+    g = np.load(GOLDEN)
+    for n in sorted({k.split(".")[0] for k in g.files} - {"linear"}):
+        x = from_bits(g[f"{n}.x"])
+        t = nv.FP4Tensor.from_bfloat16(x.cuda())
+        assert np.array_equal(t.quantized_data().cpu().numpy(), g[f"{n}.packed"].reshape(-1)), n
+        assert np.array_equal(t.scale_factors().cpu().numpy(), g[f"{n}.scales"].reshape(-1)), n
+        assert np.float32(t.global_scale().item()) == g[f"{n}.gscale"], n
+        assert np.array_equal(bits_of(t.to_bfloat16()), g[f"{n}.dequant_bf16"]), n
+
+
+def test_zeros_and_extrema(nv, oracle):
+    # fx/src/s4/nvfp4/test_quantization.cpp:250-252, test_nvfp4_quantize_te.py:113-154
+    z = torch.zeros(64, 64, dtype=torch.bfloat16)
+    t = _check_against_oracle(nv, oracle, z)
+    assert float(t.to_bfloat16().abs().max()) == 0.0
+    big = torch.full((8, 32), 3.3895313892515355e38, dtype=torch.bfloat16)
+    t = _check_against_oracle(nv, oracle, big)
+    assert torch.isfinite(t.to_bfloat16().float()).all()
+
+
+def test_empty_and_ragged_inputs(nv, oracle):
+    # n == 0 does not throw (fx/src/s4/nvfp4/test_quantization.cpp:347-358)
+    t = nv.FP4Tensor.from_bfloat16(torch.empty(0, dtype=torch.bfloat16, device="cuda"))
+    assert t.numel() == 0 and t.quantized_data().numel() == 0 and t.memory_usage() == 0
+    # numel not a multiple of 16: the tail block is completed with zeros
+    x = randn_bf16((7, 9), 21)
+    t = nv.FP4Tensor.from_bfloat16(x.cuda())
+    assert t.quantized_data().numel() == (63 + 1) // 2 and t.scale_factors().numel() == 4
+    flat = torch.zeros(64, dtype=torch.bfloat16)
+    flat[:63] = x.reshape(-1)
+    packed, scales, amax = oracle.quantize(bits_of(flat).reshape(1, 64))
+    assert np.array_equal(t.quantized_data().cpu().numpy(), packed.reshape(-1))
+    assert np.array_equal(t.scale_factors().cpu().numpy(), scales.reshape(-1))
+    assert t.to_bfloat16().shape == (7, 9)
+
+
+def test_shapes_dtypes_memory_usage(nv):
+    # fx/src/s4/nvfp4/test_tensor.cpp:47-99,152-216
+    x = randn_bf16((4, 32, 64), 30).cuda()
+    t = nv.FP4Tensor.from_bfloat16(x)
+    assert t.shape() == [4, 32, 64] and t.numel() == 4 * 32 * 64
+    assert t.quantized_data().dtype == torch.uint8 and t.scale_factors().dtype == torch.uint8
+    assert t.quantized_data().numel() == t.numel() // 2
+    assert t.scale_factors().numel() == t.numel() // 16
+    assert t.memory_usage() == t.numel() // 2 + t.numel() // 16
+    assert t.to_bfloat16().shape == x.shape
+    assert "FP4Tensor(shape=[4, 32, 64]" in repr(t)
+
+
+def test_other_modes_raise(nv):
+    x = randn_bf16((32, 32), 31).cuda()
+    for mode in (nv.QuantizationMode.block_2d, nv.QuantizationMode.per_tensor,
+                 nv.QuantizationMode.per_channel):
+        with pytest.raises(RuntimeError, match="not yet implemented"):
+            nv.FP4Tensor.from_bfloat16(x, mode)
+
+
+def test_custom_stream(nv, oracle):
+    # fx/src/s4/nvfp4/test_quantization.cpp:295-328
+    x = randn_bf16((256, 256), 32)
+    xs = x.cuda()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        t = nv.FP4Tensor.from_bfloat16(xs)
+    s.synchronize()
+    packed, scales, amax = oracle.quantize(bits_of(x))
+    assert np.array_equal(t.quantized_data().cpu().numpy(), packed.reshape(-1))
+
+
+def test_by_value_entry_points_match_reference_signature(oracle):
+    # the launcher-shaped ABI: (in, out, scales, n, global_amax, stream)
+    from blackwell_diffusion_rtx6000_5090_i2v_b200 import _native as N
+    x = randn_bf16((64, 128), 33)
+    xb = bits_of(x)
+    amax = oracle.amax(xb)
+    xd = x.cuda()
+    n = xd.numel()
+    packed = torch.empty(n // 2, dtype=torch.uint8, device="cuda")
+    scales = torch.empty(n // 16, dtype=torch.uint8, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    assert N.lib.nvfp4_quantize_bf16_amax(xd.data_ptr(), packed.data_ptr(), scales.data_ptr(), n,
+                                          amax, st) == 0
+    out = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+    assert N.lib.nvfp4_dequantize_bf16_amax(packed.data_ptr(), scales.data_ptr(), out.data_ptr(),
+                                            n, amax, st) == 0
+    p, s, _ = oracle.quantize(xb, amax)
+    assert np.array_equal(packed.cpu().numpy(), p.reshape(-1))
+    assert np.array_equal(scales.cpu().numpy(), s.reshape(-1))
+    assert np.array_equal(bits_of(out).reshape(xb.shape), oracle.dequantize_bf16(p, s, amax))
+    # misaligned input pointer is refused, not launched
+    assert N.lib.nvfp4_quantize_bf16_amax(xd.data_ptr() + 2, packed.data_ptr(), scales.data_ptr(),
+                                          n - 16, amax, st) == 2
+
+
+def test_reference_kernel_scales_pin(oracle):
+    """The reference's own TE-style kernel (compiled from the reference tree into
+    oracle/_ref) must produce the same E4M3 block scales as the oracle and as the
+    shipped kernel; its element codes are the reference's linear 4-bit code and
+    are not compared."""
+    ref = oracle.reference_te()
+    if ref is None:
+        pytest.skip("oracle/_ref/libref_quant_te.so not built")
+    from blackwell_diffusion_rtx6000_5090_i2v_b200 import nvfp4
+    for seed, gen in ((40, randn_bf16), (41, student_t_bf16), (42, outlier_weight_bf16)):
+        x = gen((192, 512), seed)
+        xb = bits_of(x)
+        amax = oracle.amax(xb)
+        xd = x.cuda()
+        n = xd.numel()
+        packed = torch.empty(n // 2, dtype=torch.uint8, device="cuda")
+        scales = torch.empty(n // 16, dtype=torch.uint8, device="cuda")
+        rc = ref.ref_te_quantize(xd.data_ptr(), packed.data_ptr(), scales.data_ptr(), n,
+                                 C.c_float(amax), None)
+        torch.cuda.synchronize()
+        assert rc == 0
+        _, s, _ = oracle.quantize(xb, amax)
+        assert np.array_equal(scales.cpu().numpy(), s.reshape(-1))
+        t = nvfp4.FP4Tensor.from_bfloat16(xd)
+        assert np.array_equal(t.scale_factors().cpu().numpy(), scales.cpu().numpy())
+
+
+def test_full_size_properties(nv):
+    """Config-2 activation size (27280 x 3072, Student-t): size-independent properties
+    instead of the oracle: round-trip error, idempotence of quantize(dequantize(q)),
+    scale bytes never NaN, amax equals torch's."""
+    x = student_t_bf16((27280, 3072), 50, device="cuda")
+    t = nv.FP4Tensor.from_bfloat16(x)
+    assert float(t.global_amax().item()) == float(x.abs().max().float().item())
+    xq = t.to_bfloat16()
+    rel = float((xq.float() - x.float()).abs().mean() / x.float().abs().mean())
+    assert rel < 0.3 and rel < 0.15
+    sc = t.scale_factors()
+    assert int(((sc & 0x7F) == 0x7F).sum()) == 0
+    # dequantized values are exactly representable, so re-quantizing with the same tensor
+    # amax reproduces the same nibbles wherever the block scale is unchanged
+    from blackwell_diffusion_rtx6000_5090_i2v_b200 import _native as N
+    n = x.numel()
+    p2 = torch.empty(n // 2, dtype=torch.uint8, device="cuda")
+    s2 = torch.empty(n // 16, dtype=torch.uint8, device="cuda")
+    N.check(N.lib.nvfp4_quantize_bf16(xq.data_ptr(), 27280, 3072, t.global_amax().data_ptr(),
+                                      p2.data_ptr(), s2.data_ptr(), None, None,
+                                      torch.cuda.current_stream().cuda_stream), "requantize")
+    same_scale = (s2 == sc)
+    assert float(same_scale.float().mean()) > 0.95
+    blk = (p2.view(-1, 8) == t.quantized_data().view(-1, 8)).all(dim=1)
+    assert bool(blk[same_scale].all())
