@@ -1,0 +1,122 @@
+"""The four NVFP4 linears of one Wan 2.2 DiT block as one preallocated runner.
+
+Call sites being accelerated: ``to_qkv`` / ``to_out`` of the self-attention
+(fx/src/s4/models/wan22/wan_transformer.py:111,129) and the feed-forward
+up (+GELU-tanh) / down projections (:185,220).  Weights are quantized once at
+construction; every step quantizes the bf16 activations (amax pass + pack
+pass) and runs the tcgen05 GEMM with bias (and GELU) fused in its epilogue.
+All buffers are allocated up front, so a step launches kernels only.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from . import _native as N
+from .nvfp4 import FP4Tensor
+
+
+@dataclass(frozen=True)
+class LinearSpec:
+    name: str
+    n: int      # out features
+    k: int      # in features
+    gelu: bool = False
+
+
+def wan_block_specs(dim: int, ffn: int) -> List[LinearSpec]:
+    return [LinearSpec("qkv", 3 * dim, dim), LinearSpec("attn_out", dim, dim),
+            LinearSpec("ffn_up", ffn, dim, gelu=True), LinearSpec("ffn_down", dim, ffn)]
+
+
+WAN22_TI2V_5B = dict(dim=3072, ffn=14336, tokens=27280)   # 1280x704, 121 frames
+WAN22_A14B = dict(dim=5120, ffn=13824, tokens=32760)      # 832x480, 81 frames
+
+
+class _QuantScratch:
+    """Reusable packed-activation buffers for an [m, k] bf16 input."""
+
+    def __init__(self, m: int, k: int, device):
+        self.m, self.k = m, k
+        self.data = torch.empty(m * k // 2, dtype=torch.uint8, device=device)
+        self.sf = torch.empty(N.lib.nvfp4_swizzled_scale_bytes(m, k), dtype=torch.uint8,
+                              device=device)
+        self.amax = torch.empty(1, dtype=torch.float32, device=device)
+        self.gscale = torch.empty(1, dtype=torch.float32, device=device)
+
+
+class WanBlockLinears:
+    """Quantized weights + scratch for the block's linears at a fixed token count."""
+
+    def __init__(self, specs: List[LinearSpec], tokens: int, weights: Dict[str, torch.Tensor],
+                 biases: Optional[Dict[str, torch.Tensor]] = None, device="cuda"):
+        self.specs = specs
+        self.tokens = tokens
+        self.device = torch.device(device)
+        self.w: Dict[str, FP4Tensor] = {}
+        self.bias: Dict[str, Optional[torch.Tensor]] = {}
+        self.act: Dict[str, _QuantScratch] = {}
+        self.out: Dict[str, torch.Tensor] = {}
+        for s in specs:
+            w = weights[s.name]
+            assert tuple(w.shape) == (s.n, s.k) and w.dtype == torch.bfloat16
+            self.w[s.name] = FP4Tensor.from_bfloat16(w.to(self.device), linear_scales=False)
+            b = biases.get(s.name) if biases else None
+            self.bias[s.name] = b.to(self.device).contiguous() if b is not None else None
+            self.act[s.name] = _QuantScratch(tokens, s.k, self.device)
+            self.out[s.name] = torch.empty(tokens, s.n, dtype=torch.bfloat16, device=self.device)
+        self.status = N.status_word(self.device)
+        self.flops_per_step = sum(2 * tokens * s.n * s.k for s in specs)
+        self.quant_bytes_per_step = sum(2.5625 * tokens * s.k for s in specs)
+        self.kernels_per_step = 3 * len(specs)  # amax + quantize + gemm per linear
+
+    def quantize(self, name: str, x: torch.Tensor, stream: int) -> None:
+        q = self.act[name]
+        N.check(N.lib.nvfp4_amax_bf16(x.data_ptr(), q.m * q.k, q.amax.data_ptr(), stream), "amax")
+        N.check(N.lib.nvfp4_quantize_bf16(x.data_ptr(), q.m, q.k, q.amax.data_ptr(),
+                                          q.data.data_ptr(), None, q.sf.data_ptr(),
+                                          q.gscale.data_ptr(), stream), "quantize")
+
+    def gemm(self, spec: LinearSpec, stream: int) -> torch.Tensor:
+        q, w, out = self.act[spec.name], self.w[spec.name], self.out[spec.name]
+        b = self.bias[spec.name]
+        N.check(N.lib.nvfp4_gemm(q.data.data_ptr(), w._data.data_ptr(), q.sf.data_ptr(),
+                                 w._scales_swz.data_ptr(), q.gscale.data_ptr(),
+                                 w._gscale.data_ptr(), q.m, spec.n, spec.k, 1.0, 0.0, None,
+                                 b.data_ptr() if b is not None else None, None,
+                                 N.ACT_GELU_TANH if spec.gelu else N.ACT_NONE, out.data_ptr(),
+                                 self.status.data_ptr(), stream), "gemm")
+        return out
+
+    def linear(self, name: str, x: torch.Tensor) -> torch.Tensor:
+        """y = act(x @ W^T + b) for the named linear; x is bf16 [tokens, k] on the device."""
+        spec = next(s for s in self.specs if s.name == name)
+        assert x.shape == (self.tokens, spec.k) and x.dtype == torch.bfloat16 and x.is_contiguous()
+        st = N.stream_ptr()
+        self.quantize(name, x, st)
+        return self.gemm(spec, st)
+
+    def step(self, inputs: Dict[str, torch.Tensor],
+             gemm_events: Optional[List[Tuple[torch.cuda.Event, torch.cuda.Event]]] = None
+             ) -> Dict[str, torch.Tensor]:
+        """One pass over the block's linears.  ``inputs`` maps a linear's name to its bf16
+        activation; ``ffn_down`` consumes ``ffn_up``'s output when not given.  When
+        ``gemm_events`` is a list, an event pair around every GEMM launch is appended."""
+        st = N.stream_ptr()
+        for s in self.specs:
+            x = inputs.get(s.name)
+            if x is None and s.name == "ffn_down":
+                x = self.out["ffn_up"]
+            self.quantize(s.name, x, st)
+            if gemm_events is not None:
+                e0 = torch.cuda.Event(enable_timing=True)
+                e1 = torch.cuda.Event(enable_timing=True)
+                e0.record()
+                self.gemm(s, st)
+                e1.record()
+                gemm_events.append((e0, e1))
+            else:
+                self.gemm(s, st)
+        return self.out

@@ -1,0 +1,72 @@
+"""Small fixed cases of the hot kernels, for timing or for a profiler capture.
+
+    python -m blackwell_diffusion_rtx6000_5090_i2v_b200.profile_case gemm --m 8192 --n 9216 --k 3072
+    python -m blackwell_diffusion_rtx6000_5090_i2v_b200.profile_case quantize --m 27280 --k 3072
+
+Each case holds well under a few GB on the device, launches the kernel
+``--iters`` times after ``--warmup`` launches, and prints the CUDA-event time.
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+from . import _native as N
+from .nvfp4 import FP4Tensor, fp4_gemm
+from .synthetic import outlier_weight_bf16, student_t_bf16
+
+
+def _time(fn, warmup, iters):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["gemm", "quantize", "amax"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=9216)
+    ap.add_argument("--k", type=int, default=3072)
+    ap.add_argument("--gelu", action="store_true")
+    ap.add_argument("--bias", action="store_true")
+    ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--iters", type=int, default=3)
+    a = ap.parse_args()
+    torch.cuda.set_device(0)
+    x = student_t_bf16((a.m, a.k), 7, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    if a.kernel == "gemm":
+        w = outlier_weight_bf16((a.n, a.k), 8, device="cuda")
+        qa = FP4Tensor.from_bfloat16(x, linear_scales=False)
+        qb = FP4Tensor.from_bfloat16(w, linear_scales=False)
+        out = torch.empty(a.m, a.n, dtype=torch.bfloat16, device="cuda")
+        bias = torch.zeros(a.n, dtype=torch.bfloat16, device="cuda") if a.bias else None
+        ms = _time(lambda: fp4_gemm(qa, qb, out=out, gelu=a.gelu, bias=bias), a.warmup, a.iters)
+        N.check_status()
+        print(f"gemm M={a.m} N={a.n} K={a.k}: {ms:.4f} ms, "
+              f"{2.0 * a.m * a.n * a.k / ms / 1e9:.1f} TFLOP/s")
+    else:
+        q = FP4Tensor.from_bfloat16(x, linear_scales=False)
+        if a.kernel == "quantize":
+            fn = lambda: N.lib.nvfp4_quantize_bf16(  # noqa: E731
+                x.data_ptr(), a.m, a.k, q._amax.data_ptr(), q._data.data_ptr(), None,
+                q._scales_swz.data_ptr(), q._gscale.data_ptr(), st)
+            nbytes = 2.5625 * a.m * a.k
+        else:
+            fn = lambda: N.lib.nvfp4_amax_bf16(x.data_ptr(), a.m * a.k, q._amax.data_ptr(), st)  # noqa: E731
+            nbytes = 2.0 * a.m * a.k
+        ms = _time(fn, a.warmup, a.iters)
+        print(f"{a.kernel} [{a.m}, {a.k}]: {ms:.4f} ms, {nbytes / ms / 1e6:.1f} GB/s")
+
+
+if __name__ == "__main__":
+    main()
