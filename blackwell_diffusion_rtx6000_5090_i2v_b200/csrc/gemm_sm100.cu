@@ -5,16 +5,22 @@
 // One persistent CTA per SM walks 128x256 output tiles.  Roles by warp:
 //   warp 0     producer: TMA loads of the packed A/B tiles (128-byte swizzle) and
 //              bulk copies of the pre-swizzled scale atoms into a 4-stage ring
-//   warp 1     tensor-core issuer: tcgen05.cp moves the scale atoms into tensor
-//              memory, tcgen05.mma kind::mxf4nvf4 (16-element blocks, UE4M3
-//              scales) accumulates fp32 in tensor memory
+//   warp 1     tensor-core issuer: tcgen05.mma kind::mxf4nvf4 (16-element blocks,
+//              UE4M3 scales) accumulates fp32 in tensor memory
 //   warps 2-5  epilogue: tcgen05.ld of the accumulator, fused scale / bias /
 //              GELU-tanh / gate / residual, bf16 stores
+//   warps 6-9  scale-factor movers: read a stage's scale atoms from shared
+//              memory and write them into tensor memory with tcgen05.st
+//
+// The scale factors go through registers and tcgen05.st rather than
+// tcgen05.cp: measured on B200, every tcgen05.cp costs the tensor pipe about
+// 45 cycles whatever its size, and a 128x256 tile needs three per MMA, which
+// capped the kernel near 3.4 PFLOP/s; tcgen05.st runs beside the MMAs.
 //
 // Tensor memory (512 columns): two 256-column accumulators at columns 0 and
-// 192 that overlap in [192,256), and the scale factors at [448,512).  The
-// epilogue drains the overlapping 64 columns first and then lets the issuer
-// start the next tile in the other accumulator, so all but that first chunk
+// 160 that overlap in [160,256), and two 48-column scale-factor buffers at
+// 416 and 464.  The epilogue drains the overlapping 96 columns first and then
+// lets the issuer start the next tile in the other accumulator, so the rest
 // of the epilogue runs under the next tile's main loop.
 //
 // Every wait is bounded: when a wait gives up the kernel records where in
@@ -37,12 +43,15 @@ constexpr int kSfaBytes = (BM / 128) * (BK / 64) * kSfAtomBytes;  // 2048
 constexpr int kSfbBytes = (BN / 128) * (BK / 64) * kSfAtomBytes;  // 4096
 constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;
 constexpr int kEpiThreads = 128;
+constexpr int kSfThreads = 128;
 constexpr int kTmemCols = 512;
-constexpr int kAccCol1 = 192;            // second accumulator's first column
-constexpr int kSfCol = 448;              // scale factors live in [448, 512)
-constexpr int kEpiChunk = 64;            // accumulator columns per epilogue step
+constexpr int kAccCol1 = 160;            // second accumulator's first column
+constexpr int kSfCols = 48;              // SFA 4 K-blocks x 4 + SFB 4 K-blocks x 8 columns
+constexpr int kSfCol0 = 416;             // two scale-factor buffers: [416,464) and [464,512)
+constexpr int kEpiChunk = 32;            // accumulator columns per epilogue step
+constexpr int kOverlapChunks = (256 - kAccCol1) / kEpiChunk;  // chunks shared by both accumulators
 constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 2 GHz
 
 static_assert(kSmemBytes <= 232448, "exceeds the 227 KiB per-CTA shared memory limit");
@@ -122,10 +131,6 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
                ::"r"(bar)
                : "memory");
 }
-__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t sdesc) {
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc)
-               : "memory");
-}
 __device__ __forceinline__ void tc_mma_nvf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                             uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
                                             uint32_t accumulate) {
@@ -139,27 +144,29 @@ __device__ __forceinline__ void tc_mma_nvf4(uint32_t d_tmem, uint64_t a_desc, ui
       : "memory");
 }
 
-// 32 lanes x 64 consecutive fp32 columns -> 64 registers per thread.
-__device__ __forceinline__ void tc_ld_32x64(uint32_t taddr, uint32_t (&r)[64]) {
+// 32 lanes x 32 consecutive fp32 columns -> 32 registers per thread.
+__device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
-      "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
-      "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
-        "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
-        "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]),
-        "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]),
-        "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]),
-        "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]),
-        "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]),
-        "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]),
-        "=r"(r[62]), "=r"(r[63])
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
       : "memory");
+}
+// 32 lanes x 16 / x 32 columns <- registers (scale factors into tensor memory).
+__device__ __forceinline__ void tc_st_32x16(uint32_t taddr, const uint32_t* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
+__device__ __forceinline__ void tc_st_32x32(uint32_t taddr, const uint32_t* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -172,12 +179,6 @@ __device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {
   return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
          ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
-// Descriptor of one 512-byte scale atom for tcgen05.cp: 32 rows of 16 bytes,
-// no swizzle, 8-row groups 128 bytes apart.
-__device__ __forceinline__ uint64_t desc_sf(uint32_t saddr) {
-  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(128 >> 4) << 32) | ((uint64_t)1 << 46);
-}
-
 // Instruction descriptor, kind::mxf4nvf4: A and B E2M1 (code 1) both K-major,
 // N at bits 17-22 in units of 8, UE4M3 scales (bit 23 clear), M at bits 24-28
 // in units of 16, scale-factor ids 0, K = 64 (bit 31 clear).
@@ -220,6 +221,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
   auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
   auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * kStages + b); };
   const uint32_t acc_empty_bar = bar_base + 8u * (2 * kStages + 2);
+  auto sf_full_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 3 + b); };
+  auto sf_empty_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 5 + b); };
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -233,6 +236,10 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     mbar_init(acc_full_bar(0), 1);
     mbar_init(acc_full_bar(1), 1);
     mbar_init(acc_empty_bar, kEpiThreads);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(sf_full_bar(b), kSfThreads);
+      mbar_init(sf_empty_bar(b), 1);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -293,6 +300,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       uint32_t ph = 0;
       bool ok = true;
       int t = 0;
+      uint32_t it = 0;  // stages issued so far: scale-factor buffer it & 1, its phase (it >> 1) & 1
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++t) {
         const uint32_t acc = tmem_base + ((t & 1) ? kAccCol1 : 0);
         if (t > 0) {
@@ -303,17 +311,13 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         for (int kt = 0; kt < p.k_tiles; ++kt) {
           ok = mbar_wait(full_bar(s), ph, abort_flag, p.status, 0x200 + s);
           if (!ok) break;
+          const uint32_t sb = it & 1u;
+          ok = mbar_wait(sf_full_bar(sb), (it >> 1) & 1u, abort_flag, p.status, 0x600 + sb);
+          if (!ok) break;
           tc_fence_after();
           const uint32_t st = smem_base + s * kStageBytes;
-          const uint32_t sfa_s = st + kABytes + kBBytes;
-          const uint32_t sfb_s = sfa_s + kSfaBytes;
-          const uint32_t sf_t = tmem_base + kSfCol;
-#pragma unroll
-          for (int j = 0; j < BK / 64; ++j) {
-            tc_cp_sf(sf_t + 4 * j, desc_sf(sfa_s + j * kSfAtomBytes));
-            tc_cp_sf(sf_t + 16 + 8 * j, desc_sf(sfb_s + j * kSfAtomBytes));
-            tc_cp_sf(sf_t + 16 + 8 * j + 4, desc_sf(sfb_s + kSfbBytes / 2 + j * kSfAtomBytes));
-          }
+          // columns of this stage's scales: SFA of K-block j at +4j, SFB at +16+8j
+          const uint32_t sf_t = tmem_base + kSfCol0 + sb * kSfCols;
           const uint64_t da = desc_sw128(st);
           const uint64_t db = desc_sw128(st + kABytes);
 #pragma unroll
@@ -323,6 +327,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
                         (kt | j) != 0);
           }
           tc_commit(empty_bar(s));
+          tc_commit(sf_empty_bar(sb));
+          ++it;
           if (++s == kStages) {
             s = 0;
             ph ^= 1u;
@@ -330,6 +336,49 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         }
         if (!ok) break;
         tc_commit(acc_full_bar(t & 1));
+      }
+    }
+  } else if (warp >= 6) {
+    // --------------------------------------------- scale-factor movers ----
+    // Lane l of every lane quarter holds, per 512-byte atom, the 16 bytes of rows
+    // l, l+32, l+64, l+96 (4 K-blocks each): exactly four tensor-memory columns.
+    const int q = warp & 3;
+    int s = 0;
+    uint32_t ph = 0, it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      for (int kt = 0; kt < p.k_tiles; ++kt, ++it) {
+        ok = mbar_wait(full_bar(s), ph, abort_flag, p.status, 0x500 + s);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const uint8_t* sf_s = smem_gen + s * kStageBytes + kABytes + kBBytes;
+        uint32_t v[kSfCols];
+#pragma unroll
+        for (int j = 0; j < BK / 64; ++j) {
+          const uint4 a4 = *reinterpret_cast<const uint4*>(sf_s + j * kSfAtomBytes + lane * 16);
+          const uint4 b0 = *reinterpret_cast<const uint4*>(sf_s + kSfaBytes + j * kSfAtomBytes +
+                                                           lane * 16);
+          const uint4 b1 = *reinterpret_cast<const uint4*>(sf_s + kSfaBytes + kSfbBytes / 2 +
+                                                           j * kSfAtomBytes + lane * 16);
+          v[4 * j] = a4.x; v[4 * j + 1] = a4.y; v[4 * j + 2] = a4.z; v[4 * j + 3] = a4.w;
+          v[16 + 8 * j] = b0.x; v[17 + 8 * j] = b0.y; v[18 + 8 * j] = b0.z; v[19 + 8 * j] = b0.w;
+          v[20 + 8 * j] = b1.x; v[21 + 8 * j] = b1.y; v[22 + 8 * j] = b1.z; v[23 + 8 * j] = b1.w;
+        }
+        const uint32_t sb = it & 1u;
+        ok = mbar_wait(sf_empty_bar(sb), ((it >> 1) & 1u) ^ 1u, abort_flag, p.status, 0x700 + sb);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t ta = tmem_base + ((uint32_t)(q * 32) << 16) + kSfCol0 + sb * kSfCols;
+        tc_st_32x16(ta, v);
+        tc_st_32x32(ta + 16, v + 16);
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(sf_full_bar(sb));
+        if (++s == kStages) {
+          s = 0;
+          ph ^= 1u;
+        }
       }
     }
   } else {
@@ -351,12 +400,14 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       const uint32_t acc = tmem_base + ((uint32_t)(q * 32) << 16) + (buf ? kAccCol1 : 0);
 #pragma unroll 1
       for (int ci = 0; ci < BN / kEpiChunk; ++ci) {
-        // accumulator 0 overlaps the other one in its last chunk, accumulator 1 in its first
-        const int c = buf ? ci : ((ci + 3) & 3);
-        uint32_t r[64];
-        tc_ld_32x64(acc + c * kEpiChunk, r);
+        // accumulator 0 shares its last kOverlapChunks chunks with the other accumulator,
+        // accumulator 1 its first ones: those are drained first
+        constexpr int kChunks = BN / kEpiChunk;
+        const int c = buf ? ci : (ci + kChunks - kOverlapChunks) % kChunks;
+        uint32_t r[kEpiChunk];
+        tc_ld_32x32(acc + c * kEpiChunk, r);
         tc_wait_ld();
-        if (ci == 0) {
+        if (ci == kOverlapChunks - 1) {
           tc_fence_before();
           mbar_arrive(acc_empty_bar);
         }
