@@ -48,8 +48,12 @@ constexpr int kEpiThreads = 128;
 constexpr int kSfThreads = 128;
 constexpr int kTmemCols = 512;
 constexpr int kAccCol1 = 160;            // second accumulator's first column
-constexpr int kSfCols = 48;              // SFA 4 K-blocks x 4 + SFB 4 K-blocks x 8 columns
-constexpr int kSfCol0 = 416;             // two scale-factor buffers: [416,464) and [464,512)
+constexpr int kSfCol0 = 416;             // scale factors live in [416,512)
+constexpr int kSfUnitKb = 2;             // K-blocks (MMAs) per scale-factor hand-over unit
+constexpr int kSfUnitCols = 12 * kSfUnitKb;   // per K-block: 4 columns of SFA + 8 of SFB
+constexpr int kSfRing = 96 / kSfUnitCols;     // units resident in tensor memory
+constexpr int kSfUnitsPerStage = (BK / 64) / kSfUnitKb;
+static_assert(kSfUnitKb == 1 || kSfUnitKb == 2 || kSfUnitKb == 4, "unit must divide a stage");
 constexpr int kEpiChunk = 32;            // accumulator columns per epilogue step
 constexpr int kOverlapChunks = (256 - kAccCol1) / kEpiChunk;  // chunks shared by both accumulators
 constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 2 GHz
@@ -152,18 +156,32 @@ __device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr)
       : "memory");
 }
-// 32 lanes x 16 / x 32 columns <- registers (scale factors into tensor memory).
-__device__ __forceinline__ void tc_st_32x16(uint32_t taddr, const uint32_t* v) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
-      : "memory");
+// 32 lanes x N columns <- N registers per thread (scale factors into tensor memory).
+template <int N>
+__device__ __forceinline__ void tc_st_sf(uint32_t taddr, const uint32_t* v);
+template <>
+__device__ __forceinline__ void tc_st_sf<4>(uint32_t taddr, const uint32_t* v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};"
+               ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3])
+               : "memory");
 }
-__device__ __forceinline__ void tc_st_32x32(uint32_t taddr, const uint32_t* v) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
-      : "memory");
+template <>
+__device__ __forceinline__ void tc_st_sf<8>(uint32_t taddr, const uint32_t* v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+               : "memory");
+}
+template <>
+__device__ __forceinline__ void tc_st_sf<16>(uint32_t taddr, const uint32_t* v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+               ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+               : "memory");
+}
+template <>
+__device__ __forceinline__ void tc_st_sf<32>(uint32_t taddr, const uint32_t* v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+               ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+               : "memory");
 }
 __device__ __forceinline__ void tc_wait_st() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
@@ -215,14 +233,15 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   // stage s: [A 16K][B 32K][SFA 2K][SFB 4K]; A and B start on 1024-byte boundaries
   const uint32_t bar_base = smem_base + kStages * kStageBytes;
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + kStages * kStageBytes + 128);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + kStages * kStageBytes + 132);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + kStages * kStageBytes + 240);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + kStages * kStageBytes + 244);
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
   auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * kStages + b); };
   const uint32_t acc_empty_bar = bar_base + 8u * (2 * kStages + 2);
   auto sf_full_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 3 + b); };
-  auto sf_empty_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 5 + b); };
+  auto sf_empty_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 3 + kSfRing + b); };
+  static_assert(8 * (2 * kStages + 3 + 2 * kSfRing) <= 240, "barriers overrun their area");
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -236,7 +255,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     mbar_init(acc_full_bar(0), 1);
     mbar_init(acc_full_bar(1), 1);
     mbar_init(acc_empty_bar, kEpiThreads);
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < kSfRing; ++b) {
       mbar_init(sf_full_bar(b), kSfThreads);
       mbar_init(sf_empty_bar(b), 1);
     }
@@ -300,7 +319,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       uint32_t ph = 0;
       bool ok = true;
       int t = 0;
-      uint32_t it = 0;  // stages issued so far: scale-factor buffer it & 1, its phase (it >> 1) & 1
+      uint32_t un = 0;  // scale-factor units consumed so far: ring slot un % kSfRing
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++t) {
         const uint32_t acc = tmem_base + ((t & 1) ? kAccCol1 : 0);
         if (t > 0) {
@@ -311,24 +330,30 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         for (int kt = 0; kt < p.k_tiles; ++kt) {
           ok = mbar_wait(full_bar(s), ph, abort_flag, p.status, 0x200 + s);
           if (!ok) break;
-          const uint32_t sb = it & 1u;
-          ok = mbar_wait(sf_full_bar(sb), (it >> 1) & 1u, abort_flag, p.status, 0x600 + sb);
-          if (!ok) break;
           tc_fence_after();
           const uint32_t st = smem_base + s * kStageBytes;
-          // columns of this stage's scales: SFA of K-block j at +4j, SFB at +16+8j
-          const uint32_t sf_t = tmem_base + kSfCol0 + sb * kSfCols;
           const uint64_t da = desc_sw128(st);
           const uint64_t db = desc_sw128(st + kABytes);
 #pragma unroll
-          for (int j = 0; j < BK / 64; ++j) {
-            // 64 elements = 32 bytes along K inside the swizzled row: +2 in 16-byte units
-            tc_mma_nvf4(acc, da + 2 * j, db + 2 * j, kIdesc, sf_t + 4 * j, sf_t + 16 + 8 * j,
-                        (kt | j) != 0);
+          for (int u = 0; u < kSfUnitsPerStage; ++u, ++un) {
+            const uint32_t slot = un % kSfRing;
+            ok = mbar_wait(sf_full_bar(slot), (un / kSfRing) & 1u, abort_flag, p.status,
+                           0x600 + slot);
+            if (!ok) break;
+            tc_fence_after();
+            // unit layout: SFA of its K-block i at +4i, SFB at +4*kSfUnitKb + 8i
+            const uint32_t sf_t = tmem_base + kSfCol0 + slot * kSfUnitCols;
+#pragma unroll
+            for (int i = 0; i < kSfUnitKb; ++i) {
+              const int j = u * kSfUnitKb + i;
+              // 64 elements = 32 bytes along K inside the swizzled row: +2 in 16-byte units
+              tc_mma_nvf4(acc, da + 2 * j, db + 2 * j, kIdesc, sf_t + 4 * i,
+                          sf_t + 4 * kSfUnitKb + 8 * i, (kt | j) != 0);
+            }
+            tc_commit(sf_empty_bar(slot));
           }
+          if (!ok) break;
           tc_commit(empty_bar(s));
-          tc_commit(sf_empty_bar(sb));
-          ++it;
           if (++s == kStages) {
             s = 0;
             ph ^= 1u;
@@ -344,15 +369,15 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     // l, l+32, l+64, l+96 (4 K-blocks each): exactly four tensor-memory columns.
     const int q = warp & 3;
     int s = 0;
-    uint32_t ph = 0, it = 0;
+    uint32_t ph = 0, un = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-      for (int kt = 0; kt < p.k_tiles; ++kt, ++it) {
+      for (int kt = 0; kt < p.k_tiles; ++kt) {
         ok = mbar_wait(full_bar(s), ph, abort_flag, p.status, 0x500 + s);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         const uint8_t* sf_s = smem_gen + s * kStageBytes + kABytes + kBBytes;
-        uint32_t v[kSfCols];
+        uint32_t v[12 * (BK / 64)];  // unit u, K-block i: SFA at 4i, SFB at 4*kSfUnitKb + 8i
 #pragma unroll
         for (int j = 0; j < BK / 64; ++j) {
           const uint4 a4 = *reinterpret_cast<const uint4*>(sf_s + j * kSfAtomBytes + lane * 16);
@@ -360,21 +385,28 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
                                                            lane * 16);
           const uint4 b1 = *reinterpret_cast<const uint4*>(sf_s + kSfaBytes + kSfbBytes / 2 +
                                                            j * kSfAtomBytes + lane * 16);
-          v[4 * j] = a4.x; v[4 * j + 1] = a4.y; v[4 * j + 2] = a4.z; v[4 * j + 3] = a4.w;
-          v[16 + 8 * j] = b0.x; v[17 + 8 * j] = b0.y; v[18 + 8 * j] = b0.z; v[19 + 8 * j] = b0.w;
-          v[20 + 8 * j] = b1.x; v[21 + 8 * j] = b1.y; v[22 + 8 * j] = b1.z; v[23 + 8 * j] = b1.w;
+          const int ua = (j / kSfUnitKb) * kSfUnitCols + 4 * (j % kSfUnitKb);
+          const int ub = (j / kSfUnitKb) * kSfUnitCols + 4 * kSfUnitKb + 8 * (j % kSfUnitKb);
+          v[ua] = a4.x; v[ua + 1] = a4.y; v[ua + 2] = a4.z; v[ua + 3] = a4.w;
+          v[ub] = b0.x; v[ub + 1] = b0.y; v[ub + 2] = b0.z; v[ub + 3] = b0.w;
+          v[ub + 4] = b1.x; v[ub + 5] = b1.y; v[ub + 6] = b1.z; v[ub + 7] = b1.w;
         }
-        const uint32_t sb = it & 1u;
-        ok = mbar_wait(sf_empty_bar(sb), ((it >> 1) & 1u) ^ 1u, abort_flag, p.status, 0x700 + sb);
-        ok = __all_sync(0xffffffffu, ok);
+#pragma unroll
+        for (int u = 0; u < kSfUnitsPerStage; ++u, ++un) {
+          const uint32_t slot = un % kSfRing;
+          ok = mbar_wait(sf_empty_bar(slot), ((un / kSfRing) & 1u) ^ 1u, abort_flag, p.status,
+                         0x700 + slot);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t ta = tmem_base + ((uint32_t)(q * 32) << 16) + kSfCol0 + slot * kSfUnitCols;
+          tc_st_sf<4 * kSfUnitKb>(ta, v + u * kSfUnitCols);
+          tc_st_sf<8 * kSfUnitKb>(ta + 4 * kSfUnitKb, v + u * kSfUnitCols + 4 * kSfUnitKb);
+          tc_wait_st();
+          tc_fence_before();
+          mbar_arrive(sf_full_bar(slot));
+        }
         if (!ok) break;
-        tc_fence_after();
-        const uint32_t ta = tmem_base + ((uint32_t)(q * 32) << 16) + kSfCol0 + sb * kSfCols;
-        tc_st_32x16(ta, v);
-        tc_st_32x32(ta + 16, v + 16);
-        tc_wait_st();
-        tc_fence_before();
-        mbar_arrive(sf_full_bar(sb));
         if (++s == kStages) {
           s = 0;
           ph ^= 1u;
@@ -398,18 +430,28 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       tc_fence_after();
       const int row = mt * BM + q * 32 + lane;
       const uint32_t acc = tmem_base + ((uint32_t)(q * 32) << 16) + (buf ? kAccCol1 : 0);
-#pragma unroll 1
-      for (int ci = 0; ci < BN / kEpiChunk; ++ci) {
+      // The chunks both accumulators share are read into registers first, and the issuer is
+      // released before any of them is processed.
+      constexpr int kChunks = BN / kEpiChunk;
+      uint32_t ro[kOverlapChunks][kEpiChunk];
+#pragma unroll
+      for (int ci = 0; ci < kOverlapChunks; ++ci)
+        tc_ld_32x32(acc + (buf ? ci : ci + kChunks - kOverlapChunks) * kEpiChunk, ro[ci]);
+      tc_wait_ld();
+      tc_fence_before();
+      mbar_arrive(acc_empty_bar);
+#pragma unroll
+      for (int ci = 0; ci < kChunks; ++ci) {
         // accumulator 0 shares its last kOverlapChunks chunks with the other accumulator,
-        // accumulator 1 its first ones: those are drained first
-        constexpr int kChunks = BN / kEpiChunk;
+        // accumulator 1 its first ones
         const int c = buf ? ci : (ci + kChunks - kOverlapChunks) % kChunks;
         uint32_t r[kEpiChunk];
-        tc_ld_32x32(acc + c * kEpiChunk, r);
-        tc_wait_ld();
-        if (ci == kOverlapChunks - 1) {
-          tc_fence_before();
-          mbar_arrive(acc_empty_bar);
+        if (ci < kOverlapChunks) {
+#pragma unroll
+          for (int e = 0; e < kEpiChunk; ++e) r[e] = ro[ci][e];
+        } else {
+          tc_ld_32x32(acc + c * kEpiChunk, r);
+          tc_wait_ld();
         }
         const int col0 = nt * BN + c * kEpiChunk;
         if (row < p.M) {
