@@ -2,26 +2,34 @@
 //
 //   D[M,N] bf16 = beta*C + gate[n] * act( alpha*ga*gb * sum_k (a*sfa)(b*sfb) + bias[n] )
 //
-// One persistent CTA per SM walks 128x256 output tiles.  Roles by warp:
-//   warp 0     producer: TMA loads of the packed A/B tiles (128-byte swizzle) and
-//              bulk copies of the pre-swizzled scale atoms into a 4-stage ring
-//   warp 1     tensor-core issuer: tcgen05.mma kind::mxf4nvf4 (16-element blocks,
-//              UE4M3 scales) accumulates fp32 in tensor memory
+// CTA pairs (clusters of two, one CTA per SM) walk 256x256 output tiles with
+// tcgen05.mma.cta_group::2: each CTA holds 128 rows of A, half of the B tile's
+// rows and 128 rows of the accumulator, so shared memory takes in 38 KiB and
+// feeds 32 KiB per stage instead of 54 and 48 for a lone 128x256 CTA.  Roles by
+// warp, in both CTAs unless noted:
+//   warp 0     producer: five TMA loads per stage (this CTA's A rows, B half, A
+//              scale atoms, both halves of the B scale atoms; 128-byte swizzle
+//              for A/B, one destination CTA per copy) into a 5-stage ring whose
+//              "full" barrier lives in the leader CTA
+//   warp 1     leader CTA only: per stage twelve tcgen05.cp.cta_group::2 of the
+//              scale atoms (each CTA copies from its own shared memory into its
+//              own tensor memory), four tcgen05.mma kind::mxf4nvf4 (16-element
+//              blocks, UE4M3 scales, fp32 accumulators in tensor memory) and one
+//              tcgen05.commit to both CTAs
 //   warps 2-5  epilogue: tcgen05.ld of the accumulator, fused scale / bias /
 //              GELU-tanh / gate / residual, bf16 stores
-//   warps 6-9  scale-factor movers: read a stage's scale atoms from shared
-//              memory and write them into tensor memory with tcgen05.st
 //
-// The scale factors go through registers and tcgen05.st rather than
-// tcgen05.cp: measured on B200, every tcgen05.cp costs the tensor pipe about
-// 45 cycles whatever its size, and a 128x256 tile needs three per MMA, which
-// capped the kernel near 3.4 PFLOP/s; tcgen05.st runs beside the MMAs.
+// Producer and issuer run as whole converged warps with one elected lane
+// enabled per instruction.  Measured on B200: from a one-lane divergent branch
+// a tcgen05.cp costs the thread ~46 cycles and 12 copies + 4 MMAs take 801
+// cycles; from converged code a copy costs ~8 and the same stage takes 511,
+// the time of the four MMAs alone.
 //
 // Tensor memory (512 columns): two 256-column accumulators at columns 0 and
-// 160 that overlap in [160,256), and two 48-column scale-factor buffers at
-// 416 and 464.  The epilogue drains the overlapping 96 columns first and then
-// lets the issuer start the next tile in the other accumulator, so the rest
-// of the epilogue runs under the next tile's main loop.
+// 192 that overlap in [192,256), scale factors at [448,496).  The epilogue
+// reads the overlapping 64 columns into registers first and then lets the
+// issuer start the next tile in the other accumulator, so the rest of the
+// epilogue runs under the next tile's main loop.
 //
 // Every wait is bounded: when a wait gives up the kernel records where in
 // *status, raises a CTA-wide abort flag, and every role leaves its loop so
@@ -33,27 +41,21 @@
 namespace nvfp4 {
 namespace gemm {
 
-constexpr int BM = 128;                  // tile rows (= TMEM lanes)
+constexpr int BM = 128;                  // rows per CTA (= TMEM lanes); a CTA pair covers 2*BM
 constexpr int BN = 256;                  // tile columns (= one MMA N)
 constexpr int BK = 256;                  // K elements per stage (128 bytes: one swizzle row)
-constexpr int kStages = 4;
-constexpr int kABytes = BM * BK / 2;     // 16384
-constexpr int kBBytes = BN * BK / 2;     // 32768
+constexpr int kStages = 5;
+constexpr int kABytes = BM * BK / 2;        // 16384: this CTA's 128 rows of A
+constexpr int kBBytes = (BN / 2) * BK / 2;  // 16384: this CTA's half of the B tile's rows
 constexpr int kSfaBytes = (BM / 128) * (BK / 64) * kSfAtomBytes;  // 2048
-constexpr int kSfbBytes = (BN / 128) * (BK / 64) * kSfAtomBytes;  // 4096
+constexpr int kSfbBytes = (BN / 128) * (BK / 64) * kSfAtomBytes;  // 4096: all 256 columns
 constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
-constexpr int kThreads = 320;
-constexpr int kEpiThreads = 128;
-constexpr int kSfThreads = 128;
+constexpr int kThreads = 192;
+constexpr int kEpiThreads = 128;  // per CTA
 constexpr int kTmemCols = 512;
-constexpr int kAccCol1 = 160;            // second accumulator's first column
-constexpr int kSfCol0 = 416;             // scale factors live in [416,512)
-constexpr int kSfUnitKb = 2;             // K-blocks (MMAs) per scale-factor hand-over unit
-constexpr int kSfUnitCols = 12 * kSfUnitKb;   // per K-block: 4 columns of SFA + 8 of SFB
-constexpr int kSfRing = 96 / kSfUnitCols;     // units resident in tensor memory
-constexpr int kSfUnitsPerStage = (BK / 64) / kSfUnitKb;
-static_assert(kSfUnitKb == 1 || kSfUnitKb == 2 || kSfUnitKb == 4, "unit must divide a stage");
+constexpr int kAccCol1 = 192;            // second accumulator's first column
+constexpr int kSfCol = 448;              // scale factors of one stage: 16 columns of SFA, 32 of SFB
 constexpr int kEpiChunk = 32;            // accumulator columns per epilogue step
 constexpr int kOverlapChunks = (256 - kAccCol1) / kEpiChunk;  // chunks shared by both accumulators
 constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 2 GHz
@@ -69,9 +71,24 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-               : "memory");
+// The asynchronous-unit instructions below take a predicate `on` instead of sitting in a
+// one-lane branch: issued from converged warp code with one elected lane enabled they cost
+// the warp ~8 cycles each, issued from a divergent single-lane branch ~45-75 (measured).
+__device__ __forceinline__ uint32_t elect_one() {
+  uint32_t e;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t.reg .b32 r;\n\t"
+      "elect.sync r|P, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(e));
+  return e;
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes, uint32_t on) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t"
+      "@q mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t}"
+      ::"r"(bar), "r"(bytes), "r"(on)
+      : "memory");
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -80,7 +97,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
@@ -88,6 +105,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// ---- CTA-pair (cluster of two) helpers ----
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of this CTA's shared-memory offset `addr` inside CTA `rank`
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+// arrive on a barrier given by its shared::cluster address (this CTA's or the peer's)
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)
+               : "memory");
+}
 // Bounded wait.  Returns false (after raising the abort flag and recording
 // `where`) when the barrier does not flip within kWaitCycles, or when another
 // role has already aborted.
@@ -108,43 +146,56 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// Tiled load into this CTA's shared memory whose byte count is reported to a barrier that
+// may live in either CTA of the pair (`bar` is a shared::cluster address).  One destination
+// CTA per copy: nothing is broadcast.
 __device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint32_t bar, uint32_t dst,
-                                            int x, int y) {
+                                            int x, int y, uint32_t on) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+      "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+      "@q cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];\n\t}"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(on)
       : "memory");
 }
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes,
-                                          uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
-      : "memory");
-}
-
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
 __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-               ::"r"(bar)
-               : "memory");
+// Arrive, once this thread's earlier tcgen05 operations (in both CTAs of the pair) have
+// completed, on the barrier at offset `bar` in the CTAs selected by `cta_mask`
+// (bit 0 = leader, bit 1 = peer).
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar, uint16_t cta_mask, uint32_t on) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t"
+      "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64"
+      " [%0], %1;\n\t}"
+      ::"r"(bar), "h"(cta_mask), "r"(on)
+      : "memory");
+}
+// One 512-byte scale atom (32 rows x 16 bytes) from shared to tensor memory, replicated
+// to the four lane quarters, in BOTH CTAs of the pair: each copies from its own shared
+// memory at the descriptor's offset into its own tensor memory.
+__device__ __forceinline__ void tc_cp_sf_pair(uint32_t taddr, uint64_t sdesc, uint32_t on) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t"
+      "@q tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;\n\t}"
+      ::"r"(taddr), "l"(sdesc), "r"(on)
+      : "memory");
 }
 __device__ __forceinline__ void tc_mma_nvf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                             uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
-                                            uint32_t accumulate) {
+                                            uint32_t accumulate, uint32_t on) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t"
+      "{\n\t.reg .pred p, q;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X"
+      "setp.ne.b32 q, %7, 0;\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X"
       " [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem),
-        "r"(sfb_tmem)
+        "r"(sfb_tmem), "r"(on)
       : "memory");
 }
 
@@ -155,36 +206,6 @@ __device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
       : "memory");
-}
-// 32 lanes x N columns <- N registers per thread (scale factors into tensor memory).
-template <int N>
-__device__ __forceinline__ void tc_st_sf(uint32_t taddr, const uint32_t* v);
-template <>
-__device__ __forceinline__ void tc_st_sf<4>(uint32_t taddr, const uint32_t* v) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};"
-               ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3])
-               : "memory");
-}
-template <>
-__device__ __forceinline__ void tc_st_sf<8>(uint32_t taddr, const uint32_t* v) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-               ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
-               : "memory");
-}
-template <>
-__device__ __forceinline__ void tc_st_sf<16>(uint32_t taddr, const uint32_t* v) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-               ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
-               : "memory");
-}
-template <>
-__device__ __forceinline__ void tc_st_sf<32>(uint32_t taddr, const uint32_t* v) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-               ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
-               : "memory");
-}
-__device__ __forceinline__ void tc_wait_st() {
-  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -197,11 +218,16 @@ __device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {
   return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
          ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
+// Descriptor of one scale atom for tcgen05.cp: 32 rows of 16 bytes, no swizzle, 8-row
+// groups 128 bytes apart.
+__device__ __forceinline__ uint64_t desc_sf(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(128 >> 4) << 32) | ((uint64_t)1 << 46);
+}
 // Instruction descriptor, kind::mxf4nvf4: A and B E2M1 (code 1) both K-major,
 // N at bits 17-22 in units of 8, UE4M3 scales (bit 23 clear), M at bits 24-28
 // in units of 16, scale-factor ids 0, K = 64 (bit 31 clear).
 constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
-                            ((uint32_t)(BM >> 4) << 24);
+                            ((uint32_t)((2 * BM) >> 4) << 24);  // M = 256 across the CTA pair
 
 __device__ __forceinline__ float gelu_tanh(float x) {
   // 0.5 x (1 + tanh(u)) = x * sigmoid(2u), u = sqrt(2/pi) (x + 0.044715 x^3)
@@ -227,199 +253,159 @@ struct Params {
 
 __global__ void __launch_bounds__(kThreads, 1)
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
-                  const __grid_constant__ CUtensorMap map_b, const Params p) {
+                  const __grid_constant__ CUtensorMap map_b,
+                  const __grid_constant__ CUtensorMap map_sfa,
+                  const __grid_constant__ CUtensorMap map_sfb, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  // stage s: [A 16K][B 32K][SFA 2K][SFB 4K]; A and B start on 1024-byte boundaries
+  // stage s: [A 16K][B half 16K][SFA 2K][SFB 4K]; A and B start on 1024-byte boundaries
   const uint32_t bar_base = smem_base + kStages * kStageBytes;
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + kStages * kStageBytes + 240);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + kStages * kStageBytes + 244);
-  auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
-  auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * kStages + b); };
-  const uint32_t acc_empty_bar = bar_base + 8u * (2 * kStages + 2);
-  auto sf_full_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 3 + b); };
-  auto sf_empty_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 3 + kSfRing + b); };
-  static_assert(8 * (2 * kStages + 3 + 2 * kSfRing) <= 240, "barriers overrun their area");
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + kStages * kStageBytes + 248);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + kStages * kStageBytes + 252);
+  // Barriers sit at the same offsets in both CTAs.  "leader" = waited on in CTA 0 only and
+  // fed by both CTAs; "local" = waited on in each CTA.
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };                      // leader: the stage landed in both CTAs
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };         // local: the stage's MMAs are done
+  auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * kStages + b); };  // local
+  const uint32_t acc_empty_bar = bar_base + 8u * (2 * kStages + 2);              // leader
+  static_assert(8 * (2 * kStages + 3) <= 248, "barriers overrun their area");
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int total_tiles = p.m_tiles * p.n_tiles;
+  const uint32_t rank = cluster_ctarank();      // 0 = leader of the pair
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int total_tiles = p.m_tiles * p.n_tiles;  // 256 x 256 pair tiles
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(full_bar(s), 1);
+      mbar_init(full_bar(s), 1);    // armed by the leader's producer with the bytes of BOTH CTAs
       mbar_init(empty_bar(s), 1);
     }
     mbar_init(acc_full_bar(0), 1);
     mbar_init(acc_full_bar(1), 1);
-    mbar_init(acc_empty_bar, kEpiThreads);
-    for (int b = 0; b < kSfRing; ++b) {
-      mbar_init(sf_full_bar(b), kSfThreads);
-      mbar_init(sf_empty_bar(b), 1);
-    }
+    mbar_init(acc_empty_bar, 2 * kEpiThreads / 32);  // one arrival per epilogue warp of the pair
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
                  ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols)
                  : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
+  cluster_sync_all();   // the peer's barriers exist before anything is sent to them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
     // ------------------------------------------------------- producer ----
-    if (lane == 0) {
-      int s = 0;
-      uint32_t ph = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-        const int mt = tile % p.m_tiles;
-        const int nt = tile / p.m_tiles;
-        const uint8_t* sfa_row = p.sfa + (size_t)mt * p.k_atoms * kSfAtomBytes;
-        const uint8_t* sfb_row0 = p.sfb + (size_t)(2 * nt) * p.k_atoms * kSfAtomBytes;
-        const uint8_t* sfb_row1 = sfb_row0 + (size_t)p.k_atoms * kSfAtomBytes;
-        for (int kt = 0; kt < p.k_tiles; ++kt) {
-          ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, 0x100 + s);
-          if (!ok) break;
-          const uint32_t st = smem_base + s * kStageBytes;
-          mbar_expect_tx(full_bar(s), kStageBytes);
-          tma_load_2d(&map_a, full_bar(s), st, kt * (BK / 2), mt * BM);
-          tma_load_2d(&map_b, full_bar(s), st + kABytes, kt * (BK / 2), nt * BN);
-          const size_t koff = (size_t)kt * (BK / 64) * kSfAtomBytes;
-          bulk_load(st + kABytes + kBBytes, sfa_row + koff, kSfaBytes, full_bar(s));
-          bulk_load(st + kABytes + kBBytes + kSfaBytes, sfb_row0 + koff, kSfbBytes / 2,
-                    full_bar(s));
-          bulk_load(st + kABytes + kBBytes + kSfaBytes + kSfbBytes / 2, sfb_row1 + koff,
-                    kSfbBytes / 2, full_bar(s));
-          if (++s == kStages) {
-            s = 0;
-            ph ^= 1u;
-          }
-        }
-      }
-      if (!ok) {
-        // let copies already in flight land before the CTA's memory is released
-        const long long t0 = clock64();
-        while (clock64() - t0 < 2000000LL) {
-        }
-      }
-    }
-  } else if (warp == 1) {
-    // -------------------------------------------------- tensor-core issuer ----
-    if (lane == 0) {
-      int s = 0;
-      uint32_t ph = 0;
-      bool ok = true;
-      int t = 0;
-      uint32_t un = 0;  // scale-factor units consumed so far: ring slot un % kSfRing
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++t) {
-        const uint32_t acc = tmem_base + ((t & 1) ? kAccCol1 : 0);
-        if (t > 0) {
-          ok = mbar_wait(acc_empty_bar, (uint32_t)(t - 1) & 1u, abort_flag, p.status, 0x300);
-          if (!ok) break;
-          tc_fence_after();
-        }
-        for (int kt = 0; kt < p.k_tiles; ++kt) {
-          ok = mbar_wait(full_bar(s), ph, abort_flag, p.status, 0x200 + s);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t st = smem_base + s * kStageBytes;
-          const uint64_t da = desc_sw128(st);
-          const uint64_t db = desc_sw128(st + kABytes);
-#pragma unroll
-          for (int u = 0; u < kSfUnitsPerStage; ++u, ++un) {
-            const uint32_t slot = un % kSfRing;
-            ok = mbar_wait(sf_full_bar(slot), (un / kSfRing) & 1u, abort_flag, p.status,
-                           0x600 + slot);
-            if (!ok) break;
-            tc_fence_after();
-            // unit layout: SFA of its K-block i at +4i, SFB at +4*kSfUnitKb + 8i
-            const uint32_t sf_t = tmem_base + kSfCol0 + slot * kSfUnitCols;
-#pragma unroll
-            for (int i = 0; i < kSfUnitKb; ++i) {
-              const int j = u * kSfUnitKb + i;
-              // 64 elements = 32 bytes along K inside the swizzled row: +2 in 16-byte units
-              tc_mma_nvf4(acc, da + 2 * j, db + 2 * j, kIdesc, sf_t + 4 * i,
-                          sf_t + 4 * kSfUnitKb + 8 * i, (kt | j) != 0);
-            }
-            tc_commit(sf_empty_bar(slot));
-          }
-          if (!ok) break;
-          tc_commit(empty_bar(s));
-          if (++s == kStages) {
-            s = 0;
-            ph ^= 1u;
-          }
-        }
-        if (!ok) break;
-        tc_commit(acc_full_bar(t & 1));
-      }
-    }
-  } else if (warp >= 6) {
-    // --------------------------------------------- scale-factor movers ----
-    // Lane l of every lane quarter holds, per 512-byte atom, the 16 bytes of rows
-    // l, l+32, l+64, l+96 (4 K-blocks each): exactly four tensor-memory columns.
-    const int q = warp & 3;
+    // The whole warp walks the loop; one elected lane is enabled on each copy.
+    const uint32_t on = elect_one();
     int s = 0;
-    uint32_t ph = 0, un = 0;
+    uint32_t ph = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+    for (int tile = pair; ok && tile < total_tiles; tile += num_pairs) {
+      const int mt = tile % p.m_tiles;
+      const int nt = tile / p.m_tiles;
+      // first scale atom of this CTA's A rows / of the tile's two 128-column halves
+      const int sfa_atom = (2 * mt + (int)rank) * p.k_atoms;
+      const int sfb_atom0 = (2 * nt) * p.k_atoms;
+      const int sfb_atom1 = sfb_atom0 + p.k_atoms;
       for (int kt = 0; kt < p.k_tiles; ++kt) {
-        ok = mbar_wait(full_bar(s), ph, abort_flag, p.status, 0x500 + s);
+        ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, 0x100 + s);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        const uint8_t* sf_s = smem_gen + s * kStageBytes + kABytes + kBBytes;
-        uint32_t v[12 * (BK / 64)];  // unit u, K-block i: SFA at 4i, SFB at 4*kSfUnitKb + 8i
-#pragma unroll
-        for (int j = 0; j < BK / 64; ++j) {
-          const uint4 a4 = *reinterpret_cast<const uint4*>(sf_s + j * kSfAtomBytes + lane * 16);
-          const uint4 b0 = *reinterpret_cast<const uint4*>(sf_s + kSfaBytes + j * kSfAtomBytes +
-                                                           lane * 16);
-          const uint4 b1 = *reinterpret_cast<const uint4*>(sf_s + kSfaBytes + kSfbBytes / 2 +
-                                                           j * kSfAtomBytes + lane * 16);
-          const int ua = (j / kSfUnitKb) * kSfUnitCols + 4 * (j % kSfUnitKb);
-          const int ub = (j / kSfUnitKb) * kSfUnitCols + 4 * kSfUnitKb + 8 * (j % kSfUnitKb);
-          v[ua] = a4.x; v[ua + 1] = a4.y; v[ua + 2] = a4.z; v[ua + 3] = a4.w;
-          v[ub] = b0.x; v[ub + 1] = b0.y; v[ub + 2] = b0.z; v[ub + 3] = b0.w;
-          v[ub + 4] = b1.x; v[ub + 5] = b1.y; v[ub + 6] = b1.z; v[ub + 7] = b1.w;
-        }
-#pragma unroll
-        for (int u = 0; u < kSfUnitsPerStage; ++u, ++un) {
-          const uint32_t slot = un % kSfRing;
-          ok = mbar_wait(sf_empty_bar(slot), ((un / kSfRing) & 1u) ^ 1u, abort_flag, p.status,
-                         0x700 + slot);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t ta = tmem_base + ((uint32_t)(q * 32) << 16) + kSfCol0 + slot * kSfUnitCols;
-          tc_st_sf<4 * kSfUnitKb>(ta, v + u * kSfUnitCols);
-          tc_st_sf<8 * kSfUnitKb>(ta + 4 * kSfUnitKb, v + u * kSfUnitCols + 4 * kSfUnitKb);
-          tc_wait_st();
-          tc_fence_before();
-          mbar_arrive(sf_full_bar(slot));
-        }
-        if (!ok) break;
+        const uint32_t st = smem_base + s * kStageBytes;
+        // Everything both CTAs load for this stage completes the leader's barrier, which the
+        // leader alone arms (a remote arrive per stage stalls the issuing thread for
+        // thousands of cycles).
+        const uint32_t lead_full = mapa_u32(full_bar(s), 0);
+        mbar_expect_tx(full_bar(s), 2 * kStageBytes, rank == 0 ? on : 0u);
+        tma_load_2d(&map_a, lead_full, st, kt * (BK / 2), (2 * mt + (int)rank) * BM, on);
+        tma_load_2d(&map_b, lead_full, st + kABytes, kt * (BK / 2), nt * BN + (int)rank * (BN / 2),
+                    on);
+        tma_load_2d(&map_sfa, lead_full, st + kABytes + kBBytes, 0, sfa_atom + kt * (BK / 64), on);
+        tma_load_2d(&map_sfb, lead_full, st + kABytes + kBBytes + kSfaBytes, 0,
+                    sfb_atom0 + kt * (BK / 64), on);
+        tma_load_2d(&map_sfb, lead_full, st + kABytes + kBBytes + kSfaBytes + kSfbBytes / 2, 0,
+                    sfb_atom1 + kt * (BK / 64), on);
         if (++s == kStages) {
           s = 0;
           ph ^= 1u;
         }
       }
     }
+    if (!ok) {
+      // let copies already in flight land before the CTA's memory is released
+      const long long t0 = clock64();
+      while (clock64() - t0 < 2000000LL) {
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- tensor-core issuer (leader CTA; the peer's warp idles) ----
+    // Per stage: twelve scale-atom copies and four MMAs for the pair, then one commit.
+    // Copies and MMAs of one thread execute in issue order, so the single scale buffer
+    // needs no barrier of its own.
+    if (rank == 0) {
+      const uint32_t on = elect_one();
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      int t = 0;
+      const uint32_t sfa_t = tmem_base + kSfCol;        // SFA of K-block j at +4j
+      const uint32_t sfb_t = tmem_base + kSfCol + 16;   // SFB of K-block j at +8j (two halves)
+      for (int tile = pair; ok && tile < total_tiles; tile += num_pairs, ++t) {
+        const uint32_t acc = tmem_base + ((t & 1) ? kAccCol1 : 0);
+        if (t > 0) {
+          ok = mbar_wait(acc_empty_bar, (uint32_t)(t - 1) & 1u, abort_flag, p.status, 0x300);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+        }
+        for (int kt = 0; kt < p.k_tiles; ++kt) {
+          ok = mbar_wait(full_bar(s), ph, abort_flag, p.status, 0x200 + s);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t st = smem_base + s * kStageBytes;
+          const uint32_t sfa_s = st + kABytes + kBBytes;
+          const uint32_t sfb_s = sfa_s + kSfaBytes;
+#pragma unroll
+          for (int j = 0; j < BK / 64; ++j) {
+            tc_cp_sf_pair(sfa_t + 4 * j, desc_sf(sfa_s + j * kSfAtomBytes), on);
+            tc_cp_sf_pair(sfb_t + 8 * j, desc_sf(sfb_s + j * kSfAtomBytes), on);
+            tc_cp_sf_pair(sfb_t + 8 * j + 4, desc_sf(sfb_s + kSfbBytes / 2 + j * kSfAtomBytes), on);
+          }
+          const uint64_t da = desc_sw128(st);
+          const uint64_t db = desc_sw128(st + kABytes);
+#pragma unroll
+          for (int j = 0; j < BK / 64; ++j) {
+            // 64 elements = 32 bytes along K inside the swizzled row: +2 in 16-byte units
+            tc_mma_nvf4(acc, da + 2 * j, db + 2 * j, kIdesc, sfa_t + 4 * j, sfb_t + 8 * j,
+                        (kt | j) != 0, on);
+          }
+          tc_commit_pair(empty_bar(s), 3, on);   // both CTAs' producers may refill the stage
+          if (++s == kStages) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+        if (!ok) break;
+        tc_commit_pair(acc_full_bar(t & 1), 3, on);
+      }
+    }
   } else {
     // ------------------------------------------------------- epilogue ----
     const int q = warp & 3;  // tensor-memory lane quarter this warp may read
     const float scale = p.alpha * (p.ga ? __ldg(p.ga) : 1.0f) * (p.gb ? __ldg(p.gb) : 1.0f);
+    const uint32_t lead_acc_empty = mapa_u32(acc_empty_bar, 0);
     bool ok = true;
     int t = 0;
-    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++t) {
+    for (int tile = pair; ok && tile < total_tiles; tile += num_pairs, ++t) {
       const int mt = tile % p.m_tiles;
       const int nt = tile / p.m_tiles;
       const int buf = t & 1;
@@ -428,7 +414,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const int row = mt * BM + q * 32 + lane;
+      const int row = (2 * mt + (int)rank) * BM + q * 32 + lane;
       const uint32_t acc = tmem_base + ((uint32_t)(q * 32) << 16) + (buf ? kAccCol1 : 0);
       // The chunks both accumulators share are read into registers first, and the issuer is
       // released before any of them is processed.
@@ -439,7 +425,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         tc_ld_32x32(acc + (buf ? ci : ci + kChunks - kOverlapChunks) * kEpiChunk, ro[ci]);
       tc_wait_ld();
       tc_fence_before();
-      mbar_arrive(acc_empty_bar);
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(lead_acc_empty);
 #pragma unroll
       for (int ci = 0; ci < kChunks; ++ci) {
         // accumulator 0 shares its last kOverlapChunks chunks with the other accumulator,
@@ -505,11 +492,15 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     }
   }
 
+
+  // Both CTAs of the pair must be done with each other's barriers and with the shared
+  // tensor-memory allocation before either releases it.
   tc_fence_before();
   __syncthreads();
+  cluster_sync_all();
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "r"(kTmemCols)
                  : "memory");
   }
@@ -547,6 +538,20 @@ static bool make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k
   cuuint32_t elem[2] = {1u, 1u};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
             elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Tensor map over a swizzled scale buffer seen as [atoms][128 x u32]: box of four atoms
+// (one pipeline stage of one 128-row tile, 2048 contiguous bytes), no swizzle.
+static bool make_sf_map(CUtensorMap* map, const void* base, int64_t atoms) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {128u, (cuuint64_t)atoms};
+  cuuint64_t strides[1] = {(cuuint64_t)kSfAtomBytes};
+  cuuint32_t box[2] = {128u, (cuuint32_t)(BK / 64)};
+  cuuint32_t elem[2] = {1u, 1u};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box,
+            elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -588,9 +593,11 @@ extern "C" int nvfp4_gemm(const uint8_t* a_packed, const uint8_t* b_packed,
   int rc = check_device_sm100();
   if (rc != NVFP4_OK) return rc;
 
-  CUtensorMap map_a, map_b;
+  CUtensorMap map_a, map_b, map_sfa, map_sfb;
   if (!gemm::make_map(&map_a, a_packed, M, K / 2, gemm::BM) ||
-      !gemm::make_map(&map_b, b_packed, N, K / 2, gemm::BN))
+      !gemm::make_map(&map_b, b_packed, N, K / 2, gemm::BN / 2) ||
+      !gemm::make_sf_map(&map_sfa, a_scales_swizzled, sf_row_tiles(M) * sf_k_atoms(K)) ||
+      !gemm::make_sf_map(&map_sfb, b_scales_swizzled, sf_row_tiles(N) * sf_k_atoms(K)))
     return NVFP4_ERR_LAUNCH_FAILED;
 
   gemm::Params p;
@@ -608,7 +615,7 @@ extern "C" int nvfp4_gemm(const uint8_t* a_packed, const uint8_t* b_packed,
   p.M = (int)M;
   p.N = (int)N;
   p.K = (int)K;
-  p.m_tiles = (int)((M + gemm::BM - 1) / gemm::BM);
+  p.m_tiles = (int)((M + 2 * gemm::BM - 1) / (2 * gemm::BM));  // 256-row pair tiles
   p.n_tiles = (int)((N + gemm::BN - 1) / gemm::BN);
   p.k_tiles = (int)((K + gemm::BK - 1) / gemm::BK);
   p.k_atoms = (int)sf_k_atoms(K);
@@ -623,10 +630,25 @@ extern "C" int nvfp4_gemm(const uint8_t* a_packed, const uint8_t* b_packed,
       return NVFP4_ERR_LAUNCH_FAILED;
     attr_set[dev] = true;
   }
+  // one CTA pair (cluster of two) per pair of SMs, each pair walking 256x256 tiles
   const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles;
-  const int sms = gemm::sm_count();
-  const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-  gemm::nvfp4_gemm_kernel<<<grid, gemm::kThreads, gemm::kSmemBytes,
-                            reinterpret_cast<cudaStream_t>(stream)>>>(map_a, map_b, p);
+  const int max_pairs = gemm::sm_count() / 2;
+  const unsigned pairs = (unsigned)(tiles < max_pairs ? tiles : max_pairs);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  cfg.blockDim = dim3(gemm::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = gemm::kSmemBytes;
+  cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, gemm::nvfp4_gemm_kernel, map_a, map_b, map_sfa, map_sfb, p) != cudaSuccess) {
+    cudaGetLastError();
+    return NVFP4_ERR_LAUNCH_FAILED;
+  }
   return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_ERR_LAUNCH_FAILED;
 }
