@@ -50,14 +50,14 @@ constexpr int kBBytes = (BN / 2) * BK / 2;  // 16384: this CTA's half of the B t
 constexpr int kSfaBytes = (BM / 128) * (BK / 64) * kSfAtomBytes;  // 2048
 constexpr int kSfbBytes = (BN / 128) * (BK / 64) * kSfAtomBytes;  // 4096: all 256 columns
 constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr int kEpiSlabBytes = 32 * 128;    // 32 rows x 64 bf16 columns, one TMA store
+constexpr int kEpiBytes = 4 * 2 * kEpiSlabBytes;  // two slabs for each of the four epilogue warps
+constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*align slack*/ + 256 /*barriers*/;
 constexpr int kThreads = 192;
 constexpr int kEpiThreads = 128;  // per CTA
 constexpr int kTmemCols = 512;
 constexpr int kAccCol1 = 192;            // second accumulator's first column
 constexpr int kSfCol = 448;              // scale factors of one stage: 16 columns of SFA, 32 of SFB
-constexpr int kEpiChunk = 32;            // accumulator columns per epilogue step
-constexpr int kOverlapChunks = (256 - kAccCol1) / kEpiChunk;  // chunks shared by both accumulators
 constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 2 GHz
 
 static_assert(kSmemBytes <= 232448, "exceeds the 227 KiB per-CTA shared memory limit");
@@ -158,6 +158,16 @@ __device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint32_t bar
       ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(on)
       : "memory");
 }
+// Tiled store of a shared-memory slab to global memory (clipped at the tensor's edges).
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y,
+                                             uint32_t on) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %4, 0;\n\t"
+      "@q cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];\n\t}"
+      ::"l"(map), "r"(src), "r"(x), "r"(y), "r"(on)
+      : "memory");
+}
+
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
@@ -255,14 +265,18 @@ __global__ void __launch_bounds__(kThreads, 1)
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
                   const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ CUtensorMap map_sfa,
-                  const __grid_constant__ CUtensorMap map_sfb, const Params p) {
+                  const __grid_constant__ CUtensorMap map_sfb,
+                  const __grid_constant__ CUtensorMap map_d, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   // stage s: [A 16K][B half 16K][SFA 2K][SFB 4K]; A and B start on 1024-byte boundaries
-  const uint32_t bar_base = smem_base + kStages * kStageBytes;
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + kStages * kStageBytes + 248);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + kStages * kStageBytes + 252);
+  // then the epilogue slabs (32 KiB, 1024-byte aligned), then the barriers
+  const uint32_t bar_base = smem_base + kStages * kStageBytes + kEpiBytes;
+  volatile int* abort_flag =
+      reinterpret_cast<volatile int*>(smem_gen + kStages * kStageBytes + kEpiBytes + 248);
+  uint32_t* tmem_slot =
+      reinterpret_cast<uint32_t*>(smem_gen + kStages * kStageBytes + kEpiBytes + 252);
   // Barriers sit at the same offsets in both CTAs.  "leader" = waited on in CTA 0 only and
   // fed by both CTAs; "local" = waited on in each CTA.
   auto full_bar = [&](int s) { return bar_base + 8u * s; };                      // leader: the stage landed in both CTAs
@@ -400,9 +414,16 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     }
   } else {
     // ------------------------------------------------------- epilogue ----
+    // Warp q owns accumulator rows 32q..32q+31 of this CTA.  64 columns at a time go
+    // through a per-warp 32 x 128-byte shared-memory slab (128-byte swizzle, so that the
+    // lane-per-row writes spread over the banks) and leave with one TMA store, which also
+    // clips at M and N.  Two slabs per warp alternate.
     const int q = warp & 3;  // tensor-memory lane quarter this warp may read
     const float scale = p.alpha * (p.ga ? __ldg(p.ga) : 1.0f) * (p.gb ? __ldg(p.gb) : 1.0f);
     const uint32_t lead_acc_empty = mapa_u32(acc_empty_bar, 0);
+    const uint32_t on = elect_one();
+    const uint32_t slab0 = smem_base + kStages * kStageBytes + (uint32_t)q * 2u * kEpiSlabBytes;
+    uint32_t slab_i = 0;
     bool ok = true;
     int t = 0;
     for (int tile = pair; ok && tile < total_tiles; tile += num_pairs, ++t) {
@@ -414,84 +435,89 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const int row = (2 * mt + (int)rank) * BM + q * 32 + lane;
+      const int row0 = (2 * mt + (int)rank) * BM + q * 32;
+      const int row = row0 + lane;
       const uint32_t acc = tmem_base + ((uint32_t)(q * 32) << 16) + (buf ? kAccCol1 : 0);
-      // The chunks both accumulators share are read into registers first, and the issuer is
-      // released before any of them is processed.
-      constexpr int kChunks = BN / kEpiChunk;
-      uint32_t ro[kOverlapChunks][kEpiChunk];
-#pragma unroll
-      for (int ci = 0; ci < kOverlapChunks; ++ci)
-        tc_ld_32x32(acc + (buf ? ci : ci + kChunks - kOverlapChunks) * kEpiChunk, ro[ci]);
-      tc_wait_ld();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(lead_acc_empty);
-#pragma unroll
-      for (int ci = 0; ci < kChunks; ++ci) {
-        // accumulator 0 shares its last kOverlapChunks chunks with the other accumulator,
-        // accumulator 1 its first ones
-        const int c = buf ? ci : (ci + kChunks - kOverlapChunks) % kChunks;
-        uint32_t r[kEpiChunk];
-        if (ci < kOverlapChunks) {
-#pragma unroll
-          for (int e = 0; e < kEpiChunk; ++e) r[e] = ro[ci][e];
-        } else {
-          tc_ld_32x32(acc + c * kEpiChunk, r);
-          tc_wait_ld();
+      constexpr int kGroups = BN / 64;   // 64-column groups; the first one processed is the
+                                         // one both accumulators share
+      static_assert(256 - kAccCol1 == 64, "the shared columns must be exactly one group");
+#pragma unroll 1
+      for (int gi = 0; gi < kGroups; ++gi) {
+        const int cg = buf ? gi : (gi + kGroups - 1) % kGroups;
+        uint32_t r[64];
+        tc_ld_32x32(acc + cg * 64, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+        tc_ld_32x32(acc + cg * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+        tc_wait_ld();
+        if (gi == 0) {
+          // the shared columns are in registers: the issuer may start the next tile
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(lead_acc_empty);
         }
-        const int col0 = nt * BN + c * kEpiChunk;
-        if (row < p.M) {
-          __nv_bfloat16* drow = p.d + (size_t)row * p.N + col0;
-          const __nv_bfloat16* crow = p.c ? p.c + (size_t)row * p.N + col0 : nullptr;
+        const int col0 = nt * BN + cg * 64;
+        const uint32_t slab = slab0 + (slab_i & 1u) * kEpiSlabBytes;
+        ++slab_i;
+        // the store that last read this slab (two groups ago) must have finished reading
+        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        __syncwarp();
+        const __nv_bfloat16* crow =
+            (p.c && row < p.M) ? p.c + (size_t)row * p.N + col0 : nullptr;
 #pragma unroll
-          for (int g = 0; g < kEpiChunk / 8; ++g) {
-            if (col0 + g * 8 < p.N) {
-              float v[8];
+        for (int g = 0; g < 8; ++g) {
+          float v[8];
 #pragma unroll
-              for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[g * 8 + e]) * scale;
-              if (p.bias) {
-                const uint4 bb = __ldg(reinterpret_cast<const uint4*>(p.bias + col0 + g * 8));
-                const uint32_t bw[4] = {bb.x, bb.y, bb.z, bb.w};
+          for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[g * 8 + e]) * scale;
+          const bool in_n = col0 + g * 8 < p.N;
+          if (p.bias && in_n) {
+            const uint4 bb = __ldg(reinterpret_cast<const uint4*>(p.bias + col0 + g * 8));
+            const uint32_t bw[4] = {bb.x, bb.y, bb.z, bb.w};
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  v[2 * e] += bf16lo_to_f32(bw[e]);
-                  v[2 * e + 1] += bf16hi_to_f32(bw[e]);
-                }
-              }
-              if (p.act == NVFP4_ACT_GELU_TANH) {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) v[e] = gelu_tanh(v[e]);
-              }
-              if (p.gate) {
-                const float4 g0 = __ldg(reinterpret_cast<const float4*>(p.gate + col0 + g * 8));
-                const float4 g1 = __ldg(reinterpret_cast<const float4*>(p.gate + col0 + g * 8 + 4));
-                v[0] *= g0.x; v[1] *= g0.y; v[2] *= g0.z; v[3] *= g0.w;
-                v[4] *= g1.x; v[5] *= g1.y; v[6] *= g1.z; v[7] *= g1.w;
-              }
-              if (crow) {
-                const uint4 cc = __ldg(reinterpret_cast<const uint4*>(crow + g * 8));
-                const uint32_t cw[4] = {cc.x, cc.y, cc.z, cc.w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  v[2 * e] += p.beta * bf16lo_to_f32(cw[e]);
-                  v[2 * e + 1] += p.beta * bf16hi_to_f32(cw[e]);
-                }
-              }
-              uint32_t o[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
-                o[e] = *reinterpret_cast<uint32_t*>(&h);
-              }
-              *reinterpret_cast<uint4*>(drow + g * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+            for (int e = 0; e < 4; ++e) {
+              v[2 * e] += bf16lo_to_f32(bw[e]);
+              v[2 * e + 1] += bf16hi_to_f32(bw[e]);
             }
           }
+          if (p.act == NVFP4_ACT_GELU_TANH) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = gelu_tanh(v[e]);
+          }
+          if (p.gate && in_n) {
+            const float4 g0 = __ldg(reinterpret_cast<const float4*>(p.gate + col0 + g * 8));
+            const float4 g1 = __ldg(reinterpret_cast<const float4*>(p.gate + col0 + g * 8 + 4));
+            v[0] *= g0.x; v[1] *= g0.y; v[2] *= g0.z; v[3] *= g0.w;
+            v[4] *= g1.x; v[5] *= g1.y; v[6] *= g1.z; v[7] *= g1.w;
+          }
+          if (crow && in_n) {
+            const uint4 cc = __ldg(reinterpret_cast<const uint4*>(crow + g * 8));
+            const uint32_t cw[4] = {cc.x, cc.y, cc.z, cc.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              v[2 * e] += p.beta * bf16lo_to_f32(cw[e]);
+              v[2 * e + 1] += p.beta * bf16hi_to_f32(cw[e]);
+            }
+          }
+          uint32_t o[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+            o[e] = *reinterpret_cast<uint32_t*>(&h);
+          }
+          // row `lane` of the slab, 16-byte chunk g, at its 128-byte-swizzle position
+          const uint32_t dst = slab + (uint32_t)lane * 128u + (uint32_t)((g ^ (lane & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(o[0]), "r"(o[1]),
+                       "r"(o[2]), "r"(o[3])
+                       : "memory");
         }
+        // make the slab visible to the TMA unit, then one lane sends it
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        tma_store_2d(&map_d, slab, col0, row0, (row0 < p.M && col0 < p.N) ? on : 0u);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
       }
     }
+    // the CTA's shared memory must outlive the stores that read it
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
   }
-
 
   // Both CTAs of the pair must be done with each other's barriers and with the shared
   // tensor-memory allocation before either releases it.
@@ -555,6 +581,20 @@ static bool make_sf_map(CUtensorMap* map, const void* base, int64_t atoms) {
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Tensor map over the bf16 output [M][N]: box of 64 columns x 32 rows (one epilogue slab),
+// 128-byte swizzle.
+static bool make_d_map(CUtensorMap* map, void* base, int64_t M, int64_t N) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+  cuuint64_t strides[1] = {(cuuint64_t)N * 2u};
+  cuuint32_t box[2] = {64u, 32u};
+  cuuint32_t elem[2] = {1u, 1u};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 static int sm_count() {
   static int cached[64];
   int dev = 0;
@@ -593,11 +633,12 @@ extern "C" int nvfp4_gemm(const uint8_t* a_packed, const uint8_t* b_packed,
   int rc = check_device_sm100();
   if (rc != NVFP4_OK) return rc;
 
-  CUtensorMap map_a, map_b, map_sfa, map_sfb;
+  CUtensorMap map_a, map_b, map_sfa, map_sfb, map_d;
   if (!gemm::make_map(&map_a, a_packed, M, K / 2, gemm::BM) ||
       !gemm::make_map(&map_b, b_packed, N, K / 2, gemm::BN / 2) ||
       !gemm::make_sf_map(&map_sfa, a_scales_swizzled, sf_row_tiles(M) * sf_k_atoms(K)) ||
-      !gemm::make_sf_map(&map_sfb, b_scales_swizzled, sf_row_tiles(N) * sf_k_atoms(K)))
+      !gemm::make_sf_map(&map_sfb, b_scales_swizzled, sf_row_tiles(N) * sf_k_atoms(K)) ||
+      !gemm::make_d_map(&map_d, d_bf16, M, N))
     return NVFP4_ERR_LAUNCH_FAILED;
 
   gemm::Params p;
@@ -646,7 +687,7 @@ extern "C" int nvfp4_gemm(const uint8_t* a_packed, const uint8_t* b_packed,
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, gemm::nvfp4_gemm_kernel, map_a, map_b, map_sfa, map_sfb, p) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, gemm::nvfp4_gemm_kernel, map_a, map_b, map_sfa, map_sfb, map_d, p) != cudaSuccess) {
     cudaGetLastError();
     return NVFP4_ERR_LAUNCH_FAILED;
   }
