@@ -37,6 +37,8 @@ SIGNATURES = {
     "nvfp4_swizzle_scales": (_i, [_p, _i64, _i64, _p, _p]),
     "nvfp4_gemm": (_i, [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _f, _f, _p, _p, _p, _i, _p,
                         _p, _p]),
+    "nvfp4_linear_bf16_static": (_i, [_p, _i64, _i64, _p, _p, _p, _i64, _p, _i, _p, _p, _p]),
+    "nvfp4_linear_bf16_static_max_elements": (_i64, []),
 }
 
 for _name, (_res, _args) in SIGNATURES.items():

@@ -118,6 +118,26 @@ NVFP4_API int nvfp4_gemm(const uint8_t* a_packed, const uint8_t* b_packed, const
                float beta, const void* c_bf16, const void* bias_bf16, const float* gate_f32,
                int act, void* d_bf16, int* status_dev, void* stream);
 
+/* Has no counterpart in the reference.  One whole linear, y = act(x W^T + bias), for
+ * callers that cannot allocate device memory (code inside a region where cudaMalloc is not
+ * allowed, fixed-budget real-time loops, plug-ins handed only input and output pointers):
+ * the packed activation, its scales and the amax / tensor-scale slots live in a fixed
+ * device array inside the library (about 5 MiB, held by every GPU that loads the library
+ * until the process exits).  x is bf16 [M, K]; the weight is given pre-quantized (packed
+ * [N, K/2], swizzled scales, device tensor scale); y is bf16 [M, N]; bias may be null.
+ * Limits: M*K <= nvfp4_linear_bf16_static_max_elements() (8 Mi) and K % 32 == 0, N % 8 == 0;
+ * anything larger returns NVFP4_ERR_BAD_ARG.  The first call on each device resolves the
+ * array's device address (with that device current); make that first call outside any
+ * stream capture.  No call allocates.  All calls on a device share the one array: two calls
+ * whose kernels can overlap on the GPU (different streams without ordering) race; calls on
+ * one stream are safe, and nothing is carried from one call to the next. */
+NVFP4_API int nvfp4_linear_bf16_static(const void* x_bf16, int64_t M, int64_t K,
+                                       const uint8_t* w_packed, const uint8_t* w_scales_swizzled,
+                                       const float* w_global_scale_dev, int64_t N,
+                                       const void* bias_bf16, int act, void* y_bf16,
+                                       int* status_dev, void* stream);
+NVFP4_API int64_t nvfp4_linear_bf16_static_max_elements(void);
+
 #ifdef __cplusplus
 }
 #endif
