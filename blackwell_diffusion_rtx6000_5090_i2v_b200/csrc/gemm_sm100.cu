@@ -150,22 +150,37 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 // Tiled load into this CTA's shared memory whose byte count is reported to a barrier that
 // may live in either CTA of the pair (`bar` is a shared::cluster address).  One destination
 // CTA per copy: nothing is broadcast.
+// `policy` is an L2 eviction policy from l2_policy_evict_last/first().
 __device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint32_t bar, uint32_t dst,
-                                            int x, int y, uint32_t on) {
+                                            int x, int y, uint64_t policy, uint32_t on) {
   asm volatile(
       "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %5, 0;\n\t"
       "@q cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4}], [%2];\n\t}"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(on)
+      ".L2::cache_hint [%0], [%1, {%3, %4}], [%2], %6;\n\t}"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(on), "l"(policy)
       : "memory");
+}
+// Operands are re-read from L2 by many CTAs (keep them), the output is written once (let it
+// go first): without these hints the 500 MB output stream evicts the operands and a quarter
+// of the operand sectors miss in L2.
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
 }
 // Tiled store of a shared-memory slab to global memory (clipped at the tensor's edges).
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y,
-                                             uint32_t on) {
+                                             uint64_t policy, uint32_t on) {
   asm volatile(
       "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %4, 0;\n\t"
-      "@q cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];\n\t}"
-      ::"l"(map), "r"(src), "r"(x), "r"(y), "r"(on)
+      "@q cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint"
+      " [%0, {%2, %3}], [%1], %5;\n\t}"
+      ::"l"(map), "r"(src), "r"(x), "r"(y), "r"(on), "l"(policy)
       : "memory");
 }
 
@@ -252,6 +267,21 @@ __device__ __forceinline__ float gelu_tanh(float x) {
   return fmaf(hx, t, hx);
 }
 
+// Tile order.  Tiles are numbered so that the pairs running at one time (consecutive
+// numbers) cover a block of kRasterM tile rows by several tile columns: each A row block is
+// then swept over all columns while it is hot in L2 instead of once per column with the whole
+// of A in between (A is 195 MB at K = 14336, more than L2).
+constexpr int kRasterM = 8;
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int& mt, int& nt) {
+  const int per_group = kRasterM * n_tiles;
+  const int group = tile / per_group;
+  const int rem = tile - group * per_group;
+  const int first = group * kRasterM;
+  const int rows = min(kRasterM, m_tiles - first);
+  nt = rem / rows;
+  mt = first + (rem - nt * rows);
+}
+
 struct Params {
   const uint8_t* sfa;
   const uint8_t* sfb;
@@ -327,12 +357,13 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     // ------------------------------------------------------- producer ----
     // The whole warp walks the loop; one elected lane is enabled on each copy.
     const uint32_t on = elect_one();
+    const uint64_t keep = l2_policy_evict_last();
     int s = 0;
     uint32_t ph = 0;
     bool ok = true;
     for (int tile = pair; ok && tile < total_tiles; tile += num_pairs) {
-      const int mt = tile % p.m_tiles;
-      const int nt = tile / p.m_tiles;
+      int mt, nt;
+      tile_coords(tile, p.m_tiles, p.n_tiles, mt, nt);
       // first scale atom of this CTA's A rows / of the tile's two 128-column halves
       const int sfa_atom = (2 * mt + (int)rank) * p.k_atoms;
       const int sfb_atom0 = (2 * nt) * p.k_atoms;
@@ -347,14 +378,15 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         // thousands of cycles).
         const uint32_t lead_full = mapa_u32(full_bar(s), 0);
         mbar_expect_tx(full_bar(s), 2 * kStageBytes, rank == 0 ? on : 0u);
-        tma_load_2d(&map_a, lead_full, st, kt * (BK / 2), (2 * mt + (int)rank) * BM, on);
+        tma_load_2d(&map_a, lead_full, st, kt * (BK / 2), (2 * mt + (int)rank) * BM, keep, on);
         tma_load_2d(&map_b, lead_full, st + kABytes, kt * (BK / 2), nt * BN + (int)rank * (BN / 2),
+                    keep, on);
+        tma_load_2d(&map_sfa, lead_full, st + kABytes + kBBytes, 0, sfa_atom + kt * (BK / 64), keep,
                     on);
-        tma_load_2d(&map_sfa, lead_full, st + kABytes + kBBytes, 0, sfa_atom + kt * (BK / 64), on);
         tma_load_2d(&map_sfb, lead_full, st + kABytes + kBBytes + kSfaBytes, 0,
-                    sfb_atom0 + kt * (BK / 64), on);
+                    sfb_atom0 + kt * (BK / 64), keep, on);
         tma_load_2d(&map_sfb, lead_full, st + kABytes + kBBytes + kSfaBytes + kSfbBytes / 2, 0,
-                    sfb_atom1 + kt * (BK / 64), on);
+                    sfb_atom1 + kt * (BK / 64), keep, on);
         if (++s == kStages) {
           s = 0;
           ph ^= 1u;
@@ -430,13 +462,14 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     const float scale = p.alpha * (p.ga ? __ldg(p.ga) : 1.0f) * (p.gb ? __ldg(p.gb) : 1.0f);
     const uint32_t lead_acc_empty = mapa_u32(acc_empty_bar, 0);
     const uint32_t on = elect_one();
+    const uint64_t stream_out = l2_policy_evict_first();
     uint8_t* slab = smem_gen + kStages * kStageBytes + (warp - 2) * kEpiSlabBytes;
     const int g_first = warp >= 6 ? 2 : 0;   // this warp's groups: g_first, g_first + 1
     bool ok = true;
     int t = 0;
     for (int tile = pair; ok && tile < total_tiles; tile += num_pairs, ++t) {
-      const int mt = tile % p.m_tiles;
-      const int nt = tile / p.m_tiles;
+      int mt, nt;
+      tile_coords(tile, p.m_tiles, p.n_tiles, mt, nt);
       const int buf = t & 1;
       ok = mbar_wait(acc_full_bar(buf), (uint32_t)(t >> 1) & 1u, abort_flag, p.status, 0x400 + buf);
       // the whole warp must agree before the .sync.aligned loads below
@@ -528,7 +561,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         // make the slab visible to the TMA unit, then one lane sends it
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
-        tma_store_2d(&map_d, smem_u32(slab), col0, row0, (row0 < p.M && col0 < p.N) ? on : 0u);
+        tma_store_2d(&map_d, smem_u32(slab), col0, row0, stream_out,
+                     (row0 < p.M && col0 < p.N) ? on : 0u);
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
       }
     }
