@@ -271,7 +271,7 @@ __device__ __forceinline__ float gelu_tanh(float x) {
 // numbers) cover a block of kRasterM tile rows by several tile columns: each A row block is
 // then swept over all columns while it is hot in L2 instead of once per column with the whole
 // of A in between (A is 195 MB at K = 14336, more than L2).
-constexpr int kRasterM = 8;
+constexpr int kRasterM = 4;
 __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int& mt, int& nt) {
   const int per_group = kRasterM * n_tiles;
   const int group = tile / per_group;
