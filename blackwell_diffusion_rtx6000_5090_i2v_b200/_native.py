@@ -36,7 +36,7 @@ SIGNATURES = {
     "nvfp4_dequantize_bf16_amax": (_i, [_p, _p, _p, _i64, _f, _p]),
     "nvfp4_swizzle_scales": (_i, [_p, _i64, _i64, _p, _p]),
     "nvfp4_gemm": (_i, [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _f, _f, _p, _p, _p, _i, _p,
-                        _p, _p]),
+                        _p, _p, _p]),
     "nvfp4_linear_bf16_static": (_i, [_p, _i64, _i64, _p, _p, _p, _i64, _p, _i, _p, _p, _p]),
     "nvfp4_linear_bf16_static_max_elements": (_i64, []),
 }

@@ -70,7 +70,8 @@ class WanBlockLinears:
         self.status = N.status_word(self.device)
         self.flops_per_step = sum(2 * tokens * s.n * s.k for s in specs)
         self.quant_bytes_per_step = sum(2.5625 * tokens * s.k for s in specs)
-        self.kernels_per_step = 3 * len(specs)  # amax + quantize + gemm per linear
+        # amax + quantize + gemm per linear, minus the amax pass the ffn_up epilogue absorbs
+        self.kernels_per_step = 3 * len(specs) - (1 if {"ffn_up", "ffn_down"} <= {s.name for s in specs} else 0)
 
     def quantize(self, name: str, x: torch.Tensor, stream: int) -> None:
         q = self.act[name]
@@ -79,7 +80,16 @@ class WanBlockLinears:
                                           q.data.data_ptr(), None, q.sf.data_ptr(),
                                           q.gscale.data_ptr(), stream), "quantize")
 
-    def gemm(self, spec: LinearSpec, stream: int) -> torch.Tensor:
+    def quantize_with_amax(self, name: str, x: torch.Tensor, stream: int) -> None:
+        """Pack ``x`` using the amax already sitting in the slot (left there by the GEMM that
+        produced ``x``)."""
+        q = self.act[name]
+        N.check(N.lib.nvfp4_quantize_bf16(x.data_ptr(), q.m, q.k, q.amax.data_ptr(),
+                                          q.data.data_ptr(), None, q.sf.data_ptr(),
+                                          q.gscale.data_ptr(), stream), "quantize")
+
+    def gemm(self, spec: LinearSpec, stream: int,
+             out_amax: Optional[torch.Tensor] = None) -> torch.Tensor:
         q, w, out = self.act[spec.name], self.w[spec.name], self.out[spec.name]
         b = self.bias[spec.name]
         N.check(N.lib.nvfp4_gemm(q.data.data_ptr(), w._data.data_ptr(), q.sf.data_ptr(),
@@ -87,6 +97,7 @@ class WanBlockLinears:
                                  w._gscale.data_ptr(), q.m, spec.n, spec.k, 1.0, 0.0, None,
                                  b.data_ptr() if b is not None else None, None,
                                  N.ACT_GELU_TANH if spec.gelu else N.ACT_NONE, out.data_ptr(),
+                                 out_amax.data_ptr() if out_amax is not None else None,
                                  self.status.data_ptr(), stream), "gemm")
         return out
 
@@ -105,18 +116,23 @@ class WanBlockLinears:
         activation; ``ffn_down`` consumes ``ffn_up``'s output when not given.  When
         ``gemm_events`` is a list, an event pair around every GEMM launch is appended."""
         st = N.stream_ptr()
+        names = [s.name for s in self.specs]
+        chained = "ffn_down" in names and "ffn_up" in names and inputs.get("ffn_down") is None
         for s in self.specs:
             x = inputs.get(s.name)
-            if x is None and s.name == "ffn_down":
-                x = self.out["ffn_up"]
-            self.quantize(s.name, x, st)
+            if s.name == "ffn_down" and chained:
+                # its amax came out of the ffn_up GEMM's epilogue: one pass over the hidden
+                self.quantize_with_amax(s.name, self.out["ffn_up"], st)
+            else:
+                self.quantize(s.name, x, st)
+            amax_next = self.act["ffn_down"].amax if (s.name == "ffn_up" and chained) else None
             if gemm_events is not None:
                 e0 = torch.cuda.Event(enable_timing=True)
                 e1 = torch.cuda.Event(enable_timing=True)
                 e0.record()
-                self.gemm(s, st)
+                self.gemm(s, st, amax_next)
                 e1.record()
                 gemm_events.append((e0, e1))
             else:
-                self.gemm(s, st)
+                self.gemm(s, st, amax_next)
         return self.out

@@ -291,6 +291,7 @@ struct Params {
   const __nv_bfloat16* bias;
   const float* gate;
   __nv_bfloat16* d;
+  unsigned* d_amax;   // optional: max |D| (as stored, bf16) accumulated by atomicMax on the bits
   int* status;
   float alpha, beta;
   int M, N, K;
@@ -463,6 +464,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     const uint32_t lead_acc_empty = mapa_u32(acc_empty_bar, 0);
     const uint32_t on = elect_one();
     const uint64_t stream_out = l2_policy_evict_first();
+    __nv_bfloat162 amax2 = __floats2bfloat162_rn(0.0f, 0.0f);   // running max |D| of this thread
     uint8_t* slab = smem_gen + kStages * kStageBytes + (warp - 2) * kEpiSlabBytes;
     const int g_first = warp >= 6 ? 2 : 0;   // this warp's groups: g_first, g_first + 1
     bool ok = true;
@@ -549,10 +551,12 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
             }
           }
           uint32_t o[4];
+          const bool counted = p.d_amax && row < p.M && col0 + g * 8 < p.N;
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
             o[e] = *reinterpret_cast<uint32_t*>(&h);
+            if (counted) amax2 = __hmax2(amax2, __habs2(h));
           }
           // row `lane` of the slab, 16-byte chunk g, at its 128-byte-swizzle position
           *reinterpret_cast<uint4*>(slab + lane * 128 + ((g ^ (lane & 7)) << 4)) =
@@ -568,6 +572,12 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     }
     // the CTA's shared memory must outlive the stores that read it
     asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    if (p.d_amax) {
+      // non-negative floats order like their bit patterns: one atomic per warp per launch
+      const float a = fmaxf(__bfloat162float(amax2.x), __bfloat162float(amax2.y));
+      const unsigned bits = __reduce_max_sync(0xffffffffu, __float_as_uint(a));
+      if (lane == 0 && bits != 0u) atomicMax(p.d_amax, bits);
+    }
   }
 
   // Both CTAs of the pair must be done with each other's barriers and with the shared
@@ -669,7 +679,7 @@ extern "C" int nvfp4_gemm(const uint8_t* a_packed, const uint8_t* b_packed,
                           const float* a_global_scale_dev, const float* b_global_scale_dev,
                           int64_t M, int64_t N, int64_t K, float alpha, float beta,
                           const void* c_bf16, const void* bias_bf16, const float* gate_f32, int act,
-                          void* d_bf16, int* status_dev, void* stream) {
+                          void* d_bf16, float* d_amax_dev, int* status_dev, void* stream) {
   if (M < 0 || N < 0 || K < 0 || N % 8 != 0 || K % 32 != 0) return NVFP4_ERR_BAD_ARG;
   if (act != NVFP4_ACT_NONE && act != NVFP4_ACT_GELU_TANH) return NVFP4_ERR_BAD_ARG;
   if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return NVFP4_ERR_BAD_ARG;
@@ -701,6 +711,7 @@ extern "C" int nvfp4_gemm(const uint8_t* a_packed, const uint8_t* b_packed,
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias_bf16);
   p.gate = gate_f32;
   p.d = reinterpret_cast<__nv_bfloat16*>(d_bf16);
+  p.d_amax = reinterpret_cast<unsigned*>(d_amax_dev);
   p.status = status_dev;
   p.alpha = alpha;
   p.beta = beta;
@@ -722,6 +733,9 @@ extern "C" int nvfp4_gemm(const uint8_t* a_packed, const uint8_t* b_packed,
       return NVFP4_ERR_LAUNCH_FAILED;
     attr_set[dev] = true;
   }
+  if (d_amax_dev && cudaMemsetAsync(d_amax_dev, 0, sizeof(float),
+                                    reinterpret_cast<cudaStream_t>(stream)) != cudaSuccess)
+    return NVFP4_ERR_LAUNCH_FAILED;
   // one CTA pair (cluster of two) per pair of SMs, each pair walking 256x256 tiles
   const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles;
   const int max_pairs = gemm::sm_count() / 2;

@@ -85,7 +85,7 @@ int nvfp4_linear_bf16_static(const void* x_bf16, int64_t M, int64_t K, const uin
   rc = nvfp4_quantize_bf16(x_bf16, M, K, amax, packed, nullptr, scales, gscale, stream);
   if (rc != NVFP4_OK) return rc;
   return nvfp4_gemm(packed, w_packed, scales, w_scales_swizzled, gscale, w_global_scale_dev, M, N,
-                    K, 1.0f, 0.0f, nullptr, bias_bf16, nullptr, act, y_bf16, status_dev, stream);
+                    K, 1.0f, 0.0f, nullptr, bias_bf16, nullptr, act, y_bf16, nullptr, status_dev, stream);
 }
 
 }  // extern "C"

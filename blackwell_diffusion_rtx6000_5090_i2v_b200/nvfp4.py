@@ -187,7 +187,8 @@ class FP4Tensor:
 def _gemm_packed(a: FP4Tensor, b: FP4Tensor, alpha: float, beta: float,
                  c: Optional[torch.Tensor], bias: Optional[torch.Tensor],
                  gate: Optional[torch.Tensor], gelu: bool,
-                 out: Optional[torch.Tensor]) -> torch.Tensor:
+                 out: Optional[torch.Tensor],
+                 out_amax: Optional[torch.Tensor] = None) -> torch.Tensor:
     a_shape, b_shape = a.shape(), b.shape()
     if len(a_shape) != 2 or len(b_shape) != 2:
         raise RuntimeError("[s4] [nvfp4] [gemm] Inputs must be 2D matrices")
@@ -215,7 +216,7 @@ def _gemm_packed(a: FP4Tensor, b: FP4Tensor, alpha: float, beta: float,
                               N.ptr(b._gscale), M, Nn, K, float(alpha), float(beta), N.ptr(c),
                               N.ptr(bias), N.ptr(gate),
                               N.ACT_GELU_TANH if gelu else N.ACT_NONE, N.ptr(out),
-                              N.ptr(N.status_word(dev)), N.stream_ptr())
+                              N.ptr(out_amax), N.ptr(N.status_word(dev)), N.stream_ptr())
     N.check(rc, "[gemm] launch")
     return out
 
@@ -223,11 +224,15 @@ def _gemm_packed(a: FP4Tensor, b: FP4Tensor, alpha: float, beta: float,
 def fp4_gemm(A: FP4Tensor, B: FP4Tensor, alpha: float = 1.0, beta: float = 0.0, *,
              C: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
              gate: Optional[torch.Tensor] = None, gelu: bool = False,
-             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+             out: Optional[torch.Tensor] = None,
+             out_amax: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``alpha * A @ B.T + beta * C`` on pre-quantized operands
     (fx/src/s4/nvfp4/tensor.h:126-143).  The reference always passes a zero C
-    (kernel.cu:109), which is what ``C=None`` means here."""
-    return _gemm_packed(A, B, alpha, beta, C, bias, gate, gelu, out)
+    (kernel.cu:109), which is what ``C=None`` means here.  ``out_amax`` (a one-element
+    fp32 device tensor) receives max|output|, sparing the next quantizer its amax pass."""
+    if out_amax is not None and (out_amax.dtype != torch.float32 or out_amax.numel() != 1):
+        raise RuntimeError("[s4] [nvfp4] [gemm] out_amax must be a one-element float32 tensor")
+    return _gemm_packed(A, B, alpha, beta, C, bias, gate, gelu, out, out_amax)
 
 
 def gemm_fp4_quantized(A: torch.Tensor, B: torch.Tensor, alpha: float = 1.0, beta: float = 0.0,

@@ -110,13 +110,15 @@ NVFP4_API int nvfp4_swizzle_scales(const uint8_t* scales_linear, int64_t rows, i
  * [N]), gate (fp32 [N]) and C (bf16 [M,N]) may be null.  Replaces
  * blackwell_fp4_gemm_prequantized (fx/src/s4/nvfp4/kernel.cuh:13-18,
  * kernel.cu:15-159) without its M,N,K % 128 restriction: any M >= 1,
- * N % 8 == 0, K % 32 == 0.  status_dev (nullable) is a device int the kernel
- * sets non-zero if a bounded wait expires. */
+ * N % 8 == 0, K % 32 == 0.  d_amax_dev (nullable) receives max|D| over the stored bf16
+ * values by atomic max (the slot is zeroed by this call, on the stream) so that a following
+ * nvfp4_quantize_bf16 of D needs no separate amax pass.  status_dev (nullable) is a device
+ * int the kernel sets non-zero if a bounded wait expires. */
 NVFP4_API int nvfp4_gemm(const uint8_t* a_packed, const uint8_t* b_packed, const uint8_t* a_scales_swizzled,
                const uint8_t* b_scales_swizzled, const float* a_global_scale_dev,
                const float* b_global_scale_dev, int64_t M, int64_t N, int64_t K, float alpha,
                float beta, const void* c_bf16, const void* bias_bf16, const float* gate_f32,
-               int act, void* d_bf16, int* status_dev, void* stream);
+               int act, void* d_bf16, float* d_amax_dev, int* status_dev, void* stream);
 
 /* Has no counterpart in the reference.  One whole linear, y = act(x W^T + bias), for
  * callers that cannot allocate device memory (code inside a region where cudaMalloc is not

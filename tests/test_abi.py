@@ -47,15 +47,15 @@ def test_argument_validation_without_device():
     assert L.nvfp4_quantize_bf16(None, 4, 24, None, None, None, None, None, None) == 1
     assert L.nvfp4_quantize_bf16_amax(None, None, None, 17, 1.0, None) == 1
     assert L.nvfp4_gemm(None, None, None, None, None, None, 8, 12, 64, 1.0, 0.0, None, None,
-                        None, 0, None, None, None) == 1  # N % 8
+                        None, 0, None, None, None, None) == 1  # N % 8
     assert L.nvfp4_gemm(None, None, None, None, None, None, 8, 16, 48, 1.0, 0.0, None, None,
-                        None, 0, None, None, None) == 1  # K % 32
+                        None, 0, None, None, None, None) == 1  # K % 32
     assert L.nvfp4_gemm(None, None, None, None, None, None, 8, 16, 64, 1.0, 0.0, None, None,
-                        None, 7, None, None, None) == 1  # unknown activation
+                        None, 7, None, None, None, None) == 1  # unknown activation
     assert L.nvfp4_gemm(None, None, None, None, None, None, 8, 16, 64, 1.0, 0.0, None, None,
-                        None, 0, None, None, None) == 1  # null operands
+                        None, 0, None, None, None, None) == 1  # null operands
     assert L.nvfp4_gemm(None, None, None, None, None, None, 0, 16, 64, 1.0, 0.0, None, None,
-                        None, 0, None, None, None) == 0  # empty problem is a no-op
+                        None, 0, None, None, None, None) == 0  # empty problem is a no-op
     assert L.nvfp4_amax_bf16(None, 16, None, None) == 1
 
 

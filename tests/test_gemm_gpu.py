@@ -236,3 +236,18 @@ def test_ragged_n_and_k_through_linear(nv, oracle):
     assert y.shape == (37, 20)
     ref = _oracle_gemm(oracle, x, w)
     assert rel_fro(y.float().cpu(), ref) <= TOL
+
+
+def test_output_amax_fused_in_epilogue(nv):
+    """max|D| from the GEMM epilogue equals the separate amax pass bit for bit, so the next
+    quantizer produces the same bytes either way (ragged M and N, GELU)."""
+    M, N, K = 777, 1032, 512
+    a = nv.FP4Tensor.from_bfloat16(student_t_bf16((M, K), 95, device="cuda"))
+    b = nv.FP4Tensor.from_bfloat16(outlier_weight_bf16((N, K), 96, device="cuda"))
+    bias = randn_bf16((N,), 97, 0.5, device="cuda")
+    amax = torch.full((1,), 123.0, dtype=torch.float32, device="cuda")  # the call zeroes it
+    y = nv.fp4_gemm(a, b, bias=bias, gelu=True, out_amax=amax)
+    nv.check_status()
+    assert float(amax.item()) == float(y.abs().max().float().item())
+    q = nv.FP4Tensor.from_bfloat16(y)
+    assert float(q.global_amax().item()) == float(amax.item())
