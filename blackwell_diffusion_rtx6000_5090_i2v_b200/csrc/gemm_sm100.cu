@@ -55,7 +55,6 @@ constexpr int kEpiWarps = 8;
 constexpr int kEpiBytes = kEpiWarps * kEpiSlabBytes;  // one slab per epilogue warp
 constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*align slack*/ + 256 /*barriers*/;
 constexpr int kThreads = 320;          // producer, issuer, eight epilogue warps
-constexpr int kEpiThreads = 128;  // per CTA
 constexpr int kTmemCols = 512;
 constexpr int kAccCol1 = 192;            // second accumulator's first column
 constexpr int kSfCol = 448;              // scale factors of one stage: 16 columns of SFA, 32 of SFB

@@ -124,6 +124,64 @@ class FP4Tensor:
                     "[tensor] quantize")
         return self
 
+    @staticmethod
+    def from_norm_mod(x: torch.Tensor, *, weight: Optional[torch.Tensor] = None,
+                      bias: Optional[torch.Tensor] = None, scale: Optional[torch.Tensor] = None,
+                      shift: Optional[torch.Tensor] = None, rms: bool = False, eps: float = 1e-6,
+                      linear_scales: bool = False, return_normed: bool = False):
+        """Quantize ``bf16(norm(x) * weight + bias) * (1 + scale) + shift`` without ever
+        writing that tensor: the fused producer in front of the DiT block's linears
+        (fx/src/s4/models/wan22/wan_transformer.py:204-206,210,218-220).  ``x`` is bf16
+        ``[..., cols]``; the per-column vectors are fp32 ``[cols]``.  With ``return_normed`` the
+        bf16 tensor is also produced and returned beside the packed one."""
+        if x.dtype != torch.bfloat16:
+            raise RuntimeError("[s4] [nvfp4] [tensor] Input must be BFloat16")
+        if not x.is_cuda:
+            raise RuntimeError("[s4] [nvfp4] [tensor] Input must be on CUDA device")
+        cols = x.shape[-1]
+        if cols % FP4_BLOCK_SIZE != 0 or cols > 16384:
+            raise RuntimeError("[s4] [nvfp4] [tensor] fused norm needs cols % 16 == 0, cols <= 16384")
+        dev = x.device
+        vecs = []
+        for name, v in (("weight", weight), ("bias", bias), ("scale", scale), ("shift", shift)):
+            if v is not None:
+                v = v.reshape(-1)
+                if v.numel() != cols or v.dtype != torch.float32 or v.device != dev:
+                    raise RuntimeError(f"[s4] [nvfp4] [tensor] {name} must be float32 [{cols}] on {dev}")
+                v = v.contiguous()
+            vecs.append(v)
+        self = object.__new__(FP4Tensor)
+        self._shape = list(x.shape)
+        self._mode = QuantizationMode.block_1d
+        self._device = dev
+        self._numel = x.numel()
+        rows = self._numel // cols
+        self._rows, self._cols = rows, cols
+        with torch.cuda.device(dev):
+            xc = x.contiguous()
+            self._amax = torch.empty(1, dtype=torch.float32, device=dev)
+            self._gscale = torch.empty(1, dtype=torch.float32, device=dev)
+            self._data = torch.empty(rows * cols // 2, dtype=torch.uint8, device=dev)
+            self._scales = (torch.empty(rows * cols // FP4_BLOCK_SIZE, dtype=torch.uint8, device=dev)
+                            if linear_scales else None)
+            self._scales_swz = torch.empty(N.lib.nvfp4_swizzled_scale_bytes(rows, cols),
+                                           dtype=torch.uint8, device=dev)
+            stats = torch.empty(rows, 2, dtype=torch.float32, device=dev)
+            normed = torch.empty_like(xc) if return_normed else None
+            st = N.stream_ptr()
+            w_, b_, sc_, sh_ = (N.ptr(v) for v in vecs)
+            N.check(N.lib.nvfp4_norm_mod_amax_bf16(N.ptr(xc), rows, cols, w_, b_, sc_, sh_,
+                                                   1 if rms else 0, float(eps), N.ptr(stats),
+                                                   N.ptr(self._amax), N.ptr(normed), st),
+                    "[tensor] norm+amax")
+            N.check(N.lib.nvfp4_norm_mod_quantize_bf16(N.ptr(xc), rows, cols, w_, b_, sc_, sh_,
+                                                       N.ptr(stats), N.ptr(self._amax),
+                                                       N.ptr(self._data), N.ptr(self._scales),
+                                                       N.ptr(self._scales_swz),
+                                                       N.ptr(self._gscale), st),
+                    "[tensor] norm+quantize")
+        return (self, normed) if return_normed else self
+
     # ------------------------------------------------------------ access --
     def to_bfloat16(self) -> torch.Tensor:
         """Dequantize (fx/src/s4/nvfp4/tensor.h:53-72)."""

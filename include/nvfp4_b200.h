@@ -120,6 +120,30 @@ NVFP4_API int nvfp4_gemm(const uint8_t* a_packed, const uint8_t* b_packed, const
                float beta, const void* c_bf16, const void* bias_bf16, const float* gate_f32,
                int act, void* d_bf16, float* d_amax_dev, int* status_dev, void* stream);
 
+/* LayerNorm (rms = 0) or RMSNorm (rms = 1) over each row of x [rows, cols] in fp32, optional
+ * affine weight/bias [cols] and adaLN modulation (1 + scale[cols]) * y + shift[cols] (all fp32,
+ * all nullable), result rounded to bf16 -- the producer chain in front of the DiT block's QKV,
+ * cross-attention Q and FFN-up linears (fx/src/s4/models/wan22/wan_transformer.py:204-206,
+ * 210, 218-220) -- fused with the NVFP4 quantizer in two sweeps over x:
+ *   sweep 1 (nvfp4_norm_mod_amax_bf16): per-row mean and rstd into row_stats [rows, 2] and the
+ *     tensor amax of the bf16 result into amax_dev (zeroed by the call); h_out_bf16 (nullable)
+ *     additionally receives the bf16 result itself;
+ *   sweep 2 (nvfp4_norm_mod_quantize_bf16): recomputes the result from x and row_stats and
+ *     writes packed nibbles, scales (linear and/or swizzled, either nullable) and the FP32
+ *     tensor scale, exactly as nvfp4_quantize_bf16 would from the bf16 result.
+ * cols % 16 == 0 and cols <= 16384. */
+NVFP4_API int nvfp4_norm_mod_amax_bf16(const void* x_bf16, int64_t rows, int64_t cols,
+                                       const float* weight, const float* bias, const float* scale,
+                                       const float* shift, int rms, float eps, float* row_stats,
+                                       float* amax_dev, void* h_out_bf16, void* stream);
+NVFP4_API int nvfp4_norm_mod_quantize_bf16(const void* x_bf16, int64_t rows, int64_t cols,
+                                           const float* weight, const float* bias,
+                                           const float* scale, const float* shift,
+                                           const float* row_stats, const float* amax_dev,
+                                           uint8_t* packed, uint8_t* scales_linear,
+                                           uint8_t* scales_swizzled, float* global_scale_dev,
+                                           void* stream);
+
 /* Has no counterpart in the reference.  One whole linear, y = act(x W^T + bias), for
  * callers that cannot allocate device memory (code inside a region where cudaMalloc is not
  * allowed, fixed-budget real-time loops, plug-ins handed only input and output pointers):
