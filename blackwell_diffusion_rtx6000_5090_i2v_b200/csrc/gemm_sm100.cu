@@ -255,15 +255,17 @@ constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17)
                             ((uint32_t)((2 * BM) >> 4) << 24);  // M = 256 across the CTA pair
 
 __device__ __forceinline__ float gelu_tanh(float x) {
-  // 0.5 x (1 + tanh(u)), u = sqrt(2/pi) (x + 0.044715 x^3), with the hardware tanh: one
-  // special-function op per element instead of an exponential and a division (a 128x256
-  // tile per CTA is 32768 elements against 16 such ops per cycle).  Its absolute error of
-  // about 5e-4 is below the bf16 rounding of the result.
-  const float u = x * (0.7978845608028654f + 0.035677408136300125f * x * x);
-  float t;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
-  const float hx = 0.5f * x;
-  return fmaf(hx, t, hx);
+  // 0.5 x (1 + tanh(u)) = x / (1 + exp(-2u)), u = sqrt(2/pi) (x + 0.044715 x^3): one ex2 and
+  // one reciprocal, both accurate to about 1e-7 relative, so the bf16 result is the correctly
+  // rounded one except in rare near-tie cases.  (The hardware tanh is one op cheaper but
+  // its 5e-4 absolute error moves a quarter of the bf16 roundings, and the FP4 re-quantization
+  // of the FFN hidden amplifies that to a percent-level difference downstream.)  exp overflow
+  // gives 1/inf = 0, the right limit.
+  const float z = x * (-2.302208198144325f + -0.1029432395800235f * x * x);   // -2 u log2(e)
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(z));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return x * r;
 }
 
 // Tile order.  Tiles are numbered so that the pairs running at one time (consecutive

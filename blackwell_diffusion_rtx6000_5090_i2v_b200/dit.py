@@ -1,0 +1,428 @@
+"""Shape-faithful Wan 2.2 DiT step whose linears all run on the NVFP4 path.
+
+Random-initialised (no checkpoint is used) model with the block structure of
+the reference transformer (fx/src/s4/models/wan22/wan_transformer.py:189-225
+for the block, :389-441 for the step): adaLN-modulated self-attention with q/k
+RMSNorm across heads and 3-D RoPE, cross-attention over the text context, and a
+GELU-tanh feed-forward.  It exists to measure the step latency of the
+benchmark configurations and to check the NVFP4 path end to end, not as a
+model implementation: attention, RoPE and the small embedders are plain bf16
+torch ops.
+
+Two ways of evaluating a linear share the same packed weights:
+  * ``nvfp4``   -- fused norm+modulation+quantize, tcgen05 FP4 GEMM with bias /
+                   GELU / gate / residual in its epilogue (the product path);
+  * ``dequant`` -- quantize, dequantize both operands to fp32, fp32 matmul (no
+                   TF32), then the same elementwise ops in torch: the
+                   dequantize-then-matmul formulation, used as the comparison
+                   for the cosine check.  Operands stay fp32 on purpose: FP4
+                   re-quantization of the next linear's input turns a
+                   perturbation of relative size e into an error of about
+                   sqrt(e * step), so a comparison path that rounds its operands
+                   to bf16 (2^-9 per value) drifts by percents within a few
+                   linears and would measure its own rounding, not the kernel.
+
+With a process group the token sequence is sharded over the ranks (weights
+replicated) and only self-attention communicates (``ulysses.py``).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+from . import ulysses
+from .nvfp4 import FP4Tensor, fp4_gemm
+
+
+@dataclass(frozen=True)
+class WanDiTConfig:
+    dim: int
+    heads: int
+    ffn: int
+    layers: int
+    in_channels: int
+    out_channels: int
+    text_dim: int = 4096
+    freq_dim: int = 256
+    head_dim: int = 128
+    patch: Tuple[int, int, int] = (1, 2, 2)
+    eps: float = 1e-6
+    rope_theta: float = 10000.0
+
+
+# Wan2.2-TI2V-5B shape: latent [48, 31, 44, 80] -> 27280 tokens
+WAN22_TI2V_5B = WanDiTConfig(dim=3072, heads=24, ffn=14336, layers=30, in_channels=48,
+                             out_channels=48)
+# Wan2.2-A14B shape (one expert): latent [16, 21, 60, 104] -> 32760 tokens
+WAN22_A14B = WanDiTConfig(dim=5120, heads=40, ffn=13824, layers=40, in_channels=16,
+                          out_channels=16)
+
+
+def _cosine(a: torch.Tensor, b: torch.Tensor) -> float:
+    a, b = a.double().flatten(), b.double().flatten()
+    return float(torch.dot(a, b) / (a.norm() * b.norm()))
+
+
+class Timeline:
+    """Per-component device time of a step: ``mark(label)`` charges the time since the previous
+    mark to ``label``.  Events only; nothing synchronizes until :meth:`totals_ms`."""
+
+    def __init__(self):
+        self.events: List[Tuple[str, torch.cuda.Event]] = []
+
+    def mark(self, label: str) -> None:
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        self.events.append((label, e))
+
+    def totals_ms(self) -> Dict[str, float]:
+        torch.cuda.synchronize()
+        out: Dict[str, float] = {}
+        for (_, e0), (label, e1) in zip(self.events, self.events[1:]):
+            out[label] = out.get(label, 0.0) + e0.elapsed_time(e1)
+        return out
+
+
+TIMELINE: Optional[Timeline] = None     # set by the step benchmark; None costs nothing
+
+
+def _mark(label: str) -> None:
+    if TIMELINE is not None:
+        TIMELINE.mark(label)
+
+
+_E2M1 = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+
+
+def dequant_f32(t: FP4Tensor) -> torch.Tensor:
+    """fp32 ``e2m1 * (float(sf) / S_enc)`` of a packed tensor that carries linear scales, in
+    torch ops (comparison path only; formula of fx/src/s4/nvfp4/quantization_te.cu:149-160)."""
+    rows, cols = t._rows, t._cols
+    b = t.quantized_data().view(rows, cols // 2)
+    tbl = torch.tensor(_E2M1 + tuple(-v for v in _E2M1), dtype=torch.float32, device=b.device)
+    vals = torch.stack([tbl[(b & 0xF).long()], tbl[(b >> 4).long()]], dim=-1).view(rows, cols)
+    amax = t.global_amax().float()
+    fmax = torch.finfo(torch.float32).max
+    s_enc = torch.clamp(torch.tensor(448.0 * 6.0, device=b.device) / amax, max=fmax)
+    s_enc = torch.where((amax == 0) | (s_enc == 0), torch.ones_like(s_enc), s_enc)
+    sf = t.scale_factors().view(torch.float8_e4m3fn).float().view(rows, cols // 16) / s_enc
+    return (vals.view(rows, cols // 16, 16) * sf.unsqueeze(-1)).view(rows, cols)
+
+
+class PackedLinear:
+    """A linear whose weight lives only in packed NVFP4 form (bias in bf16)."""
+
+    def __init__(self, n: int, k: int, gen: torch.Generator, device, std: float = 0.02,
+                 bias: bool = True):
+        w = (torch.randn(n, k, generator=gen, device=device) * std).to(torch.bfloat16)
+        self.n, self.k = n, k
+        self.w = FP4Tensor.from_bfloat16(w, linear_scales=True)
+        self.bias = ((torch.randn(n, generator=gen, device=device) * 0.01).to(torch.bfloat16)
+                     if bias else None)
+
+    def nvfp4(self, a: FP4Tensor, **epilogue) -> torch.Tensor:
+        return fp4_gemm(a, self.w, bias=self.bias, **epilogue)
+
+    def dequant(self, x: torch.Tensor, *, gelu: bool = False, gate: Optional[torch.Tensor] = None,
+                residual: Optional[torch.Tensor] = None, reorder: bool = False) -> torch.Tensor:
+        """Quantize x, dequantize both operands, matmul: the comparison path.  ``reorder``
+        reverses the K axis of both operands -- the same sum in another order, which serves as
+        the control for how much a last-bit change in a GEMM moves the step output."""
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        xq = dequant_f32(FP4Tensor.from_bfloat16(x2, linear_scales=True))
+        wq = dequant_f32(self.w)
+        if reorder:
+            xq, wq = xq.flip(-1).contiguous(), wq.flip(-1).contiguous()
+        tf32 = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = False
+        try:
+            y = torch.matmul(xq, wq.t())
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = tf32
+        if self.bias is not None:
+            y = y + self.bias.float()
+        if gelu:
+            y = F.gelu(y, approximate="tanh")
+        if gate is not None:
+            y = y * gate
+        if residual is not None:
+            y = y + residual.float()
+        return y.to(torch.bfloat16)
+
+
+def rope_tables(cfg: WanDiTConfig, grid: Tuple[int, int, int], device) -> Tuple[torch.Tensor, torch.Tensor]:
+    """3-D rotary tables ``[L, head_dim]`` (cos, sin): per axis the 1-D table of
+    fx/src/s4/models/wan_22/wan_attention_static.py:49-58 (inverse frequencies
+    theta^(-2i/d), each frequency repeated for its pair), axes t/h/w taking 44/42/42 of the
+    128 head dims (fx/src/s4/models/wan22/wan_transformer.py:274-275,309-335)."""
+    f, h, w = grid
+    hd = cfg.head_dim
+    h_dim = w_dim = 2 * (hd // 6)
+    t_dim = hd - h_dim - w_dim
+
+    def axis(dim, n):
+        inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, dim, 2, dtype=torch.float64) / dim))
+        ang = torch.arange(n, dtype=torch.float64).unsqueeze(1) * inv.unsqueeze(0)
+        ang = ang.repeat_interleave(2, dim=1)            # [n, dim]: (a0, a0, a1, a1, ...)
+        return ang.cos().float(), ang.sin().float()
+
+    ct, st = axis(t_dim, f)
+    ch, sh = axis(h_dim, h)
+    cw, sw = axis(w_dim, w)
+    cos = torch.cat([ct.view(f, 1, 1, -1).expand(f, h, w, -1), ch.view(1, h, 1, -1).expand(f, h, w, -1),
+                     cw.view(1, 1, w, -1).expand(f, h, w, -1)], dim=-1).reshape(f * h * w, hd)
+    sin = torch.cat([st.view(f, 1, 1, -1).expand(f, h, w, -1), sh.view(1, h, 1, -1).expand(f, h, w, -1),
+                     sw.view(1, 1, w, -1).expand(f, h, w, -1)], dim=-1).reshape(f * h * w, hd)
+    return cos.to(device), sin.to(device)
+
+
+def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """x ``[L, H, D]``; pairs (even, odd) rotate by the pair's angle
+    (fx/src/s4/models/wan22/wan_transformer.py:61-75)."""
+    xf = x.float()
+    x1, x2 = xf[..., 0::2], xf[..., 1::2]
+    c, s = cos[:, None, 0::2], sin[:, None, 1::2]
+    out = torch.empty_like(xf)
+    out[..., 0::2] = x1 * c - x2 * s
+    out[..., 1::2] = x1 * s + x2 * c
+    return out.to(x.dtype)
+
+
+def rms_norm(x: torch.Tensor, gain: torch.Tensor, eps: float) -> torch.Tensor:
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * gain).to(x.dtype)
+
+
+def layer_norm(x: torch.Tensor, eps: float, weight=None, bias=None) -> torch.Tensor:
+    return F.layer_norm(x.float(), (x.shape[-1],), weight, bias, eps)
+
+
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    """``[Lq, H, D]`` x ``[Lk, H, D]`` -> ``[Lq, H, D]``, bf16, non-causal, scale 1/sqrt(D)."""
+    o = F.scaled_dot_product_attention(q.transpose(0, 1).unsqueeze(0), k.transpose(0, 1).unsqueeze(0),
+                                       v.transpose(0, 1).unsqueeze(0))
+    return o.squeeze(0).transpose(0, 1)
+
+
+class WanBlock:
+    def __init__(self, cfg: WanDiTConfig, gen: torch.Generator, device):
+        d = cfg.dim
+        self.cfg = cfg
+        self.qkv = PackedLinear(3 * d, d, gen, device)
+        self.attn_out = PackedLinear(d, d, gen, device)
+        self.cross_q = PackedLinear(d, d, gen, device)
+        self.cross_kv = PackedLinear(2 * d, d, gen, device)
+        self.cross_out = PackedLinear(d, d, gen, device)
+        self.ffn_up = PackedLinear(cfg.ffn, d, gen, device)
+        self.ffn_down = PackedLinear(d, cfg.ffn, gen, device)
+        ones = lambda: torch.ones(d, device=device)  # noqa: E731
+        self.g_q, self.g_k, self.g_cq, self.g_ck = ones(), ones(), ones(), ones()  # unit RMSNorm gains
+        self.norm2_w, self.norm2_b = ones(), torch.zeros(d, device=device)
+        self.scale_shift_table = torch.randn(6, d, generator=gen, device=device) / d ** 0.5
+        self._amax = torch.empty(1, dtype=torch.float32, device=device)
+
+    # ---------------------------------------------------------------- parts --
+    def _self_attention(self, q, k, v, cos, sin, group):
+        cfg = self.cfg
+        L = q.shape[0]
+        q = apply_rope(rms_norm(q, self.g_q, cfg.eps).view(L, cfg.heads, cfg.head_dim), cos, sin)
+        k = apply_rope(rms_norm(k, self.g_k, cfg.eps).view(L, cfg.heads, cfg.head_dim), cos, sin)
+        v = v.reshape(L, cfg.heads, cfg.head_dim)
+        _mark("qk_norm_rope")
+        if group is not None:
+            # token shards -> head shards: one packed exchange for q, k, v
+            qkv = ulysses.seq_to_heads(torch.cat([q, k, v], dim=-1), group)
+            q, k, v = qkv.split(cfg.head_dim, dim=-1)
+            _mark("exchange")
+        o = attention(q, k, v)
+        _mark("self_attention")
+        if group is not None:
+            o = ulysses.heads_to_seq(o.contiguous(), group)
+            _mark("exchange")
+        return o.reshape(L, cfg.dim)
+
+    def _cross_kv(self, ctx: torch.Tensor, mode: str):
+        cfg = self.cfg
+        kv = (self.cross_kv.nvfp4(FP4Tensor.from_bfloat16(ctx, linear_scales=False))
+              if mode == "nvfp4" else self.cross_kv.dequant(ctx, reorder=mode == "dequant_reordered"))
+        k, v = kv.chunk(2, dim=-1)
+        C = ctx.shape[0]
+        return (rms_norm(k, self.g_ck, cfg.eps).view(C, cfg.heads, cfg.head_dim),
+                v.reshape(C, cfg.heads, cfg.head_dim))
+
+    # -------------------------------------------------------------- forward --
+    def forward(self, x: torch.Tensor, ctx: torch.Tensor, temb6: torch.Tensor, cos, sin,
+                mode: str = "nvfp4", group=None) -> torch.Tensor:
+        cfg = self.cfg
+        mod = self.scale_shift_table + temb6.float()
+        shift_msa, scale_msa, gate_msa, c_shift, c_scale, c_gate = (m.contiguous() for m in mod)
+        L = x.shape[0]
+        if mode == "nvfp4":
+            _mark("other")
+            a = FP4Tensor.from_norm_mod(x, scale=scale_msa, shift=shift_msa, eps=cfg.eps)
+            _mark("norm_quantize")
+            qkv = self.qkv.nvfp4(a)
+            _mark("gemm")
+            q, k, v = qkv.chunk(3, dim=-1)
+            o = self._self_attention(q, k, v, cos, sin, group)
+            oq = FP4Tensor.from_bfloat16(o.contiguous(), linear_scales=False)
+            _mark("quantize")
+            x = self.attn_out.nvfp4(oq, gate=gate_msa, C=x, beta=1.0)
+            _mark("gemm")
+            a = FP4Tensor.from_norm_mod(x, weight=self.norm2_w, bias=self.norm2_b, eps=cfg.eps)
+            _mark("norm_quantize")
+            q = self.cross_q.nvfp4(a)
+            _mark("gemm")
+            q = rms_norm(q, self.g_cq, cfg.eps).view(L, cfg.heads, cfg.head_dim)
+            _mark("qk_norm_rope")
+            ck, cv = self._cross_kv(ctx, mode)
+            _mark("text_kv")
+            o = attention(q, ck, cv).reshape(L, cfg.dim)
+            _mark("cross_attention")
+            oq = FP4Tensor.from_bfloat16(o.contiguous(), linear_scales=False)
+            _mark("quantize")
+            x = self.cross_out.nvfp4(oq, C=x, beta=1.0)
+            _mark("gemm")
+            a = FP4Tensor.from_norm_mod(x, scale=c_scale, shift=c_shift, eps=cfg.eps)
+            _mark("norm_quantize")
+            hid = self.ffn_up.nvfp4(a, gelu=True, out_amax=self._amax)
+            _mark("gemm")
+            hq = FP4Tensor.from_bfloat16(hid, linear_scales=False, amax=self._amax)
+            _mark("quantize")
+            x = self.ffn_down.nvfp4(hq, gate=c_gate, C=x, beta=1.0)
+            _mark("gemm")
+            return x
+        # comparison path: same ops, linears by dequantize-then-matmul
+        ro = mode == "dequant_reordered"
+        h = (layer_norm(x, cfg.eps) * (1 + scale_msa) + shift_msa).to(x.dtype)
+        q, k, v = self.qkv.dequant(h, reorder=ro).chunk(3, dim=-1)
+        o = self._self_attention(q, k, v, cos, sin, group)
+        x = self.attn_out.dequant(o, gate=gate_msa, residual=x, reorder=ro)
+        h = layer_norm(x, cfg.eps, self.norm2_w, self.norm2_b).to(x.dtype)
+        q = rms_norm(self.cross_q.dequant(h, reorder=ro), self.g_cq, cfg.eps).view(L, cfg.heads, cfg.head_dim)
+        ck, cv = self._cross_kv(ctx, mode)
+        o = attention(q, ck, cv).reshape(L, cfg.dim)
+        x = self.cross_out.dequant(o, residual=x, reorder=ro)
+        h = (layer_norm(x, cfg.eps) * (1 + c_scale) + c_shift).to(x.dtype)
+        hid = self.ffn_up.dequant(h, gelu=True, reorder=ro)
+        return self.ffn_down.dequant(hid, gate=c_gate, residual=x, reorder=ro)
+
+
+class WanDiT:
+    """One denoising step of the DiT (timestep + text conditioning -> blocks -> output head)."""
+
+    def __init__(self, cfg: WanDiTConfig, device="cuda", seed: int = 1234, layers: Optional[int] = None):
+        self.cfg = cfg
+        self.device = torch.device(device)
+        gen = torch.Generator(device=self.device).manual_seed(seed)
+        d = cfg.dim
+        pt, ph, pw = cfg.patch
+        self.patch_w = (torch.randn(d, cfg.in_channels, pt, ph, pw, generator=gen, device=self.device)
+                        * 0.02).to(torch.bfloat16)
+        self.patch_b = torch.zeros(d, dtype=torch.bfloat16, device=self.device)
+        self.time_in = PackedLinear(d, cfg.freq_dim, gen, self.device)
+        self.time_hidden = PackedLinear(d, d, gen, self.device)
+        self.time_proj = PackedLinear(6 * d, d, gen, self.device)
+        self.text_in = PackedLinear(d, cfg.text_dim, gen, self.device)
+        self.text_hidden = PackedLinear(d, d, gen, self.device)
+        self.blocks: List[WanBlock] = [WanBlock(cfg, gen, self.device)
+                                       for _ in range(layers if layers is not None else cfg.layers)]
+        self.out_table = torch.randn(2, d, generator=gen, device=self.device) / d ** 0.5
+        self.proj_out = PackedLinear(cfg.out_channels * pt * ph * pw, d, gen, self.device)
+
+    def _lin(self, lin: PackedLinear, x: torch.Tensor, mode: str, **kw) -> torch.Tensor:
+        if mode == "nvfp4":
+            return lin.nvfp4(FP4Tensor.from_bfloat16(x.contiguous(), linear_scales=False),
+                             gelu=kw.get("gelu", False))
+        return lin.dequant(x, gelu=kw.get("gelu", False), reorder=mode == "dequant_reordered")
+
+    def _conditions(self, t: float, text: torch.Tensor, mode: str):
+        cfg = self.cfg
+        half = cfg.freq_dim // 2
+        freqs = torch.exp(-math.log(10000.0) * torch.arange(half, device=self.device) / half)
+        ang = t * freqs
+        t_freq = torch.cat([ang.cos(), ang.sin()]).to(torch.bfloat16).unsqueeze(0)   # [1, 256]
+        temb = self._lin(self.time_hidden, F.silu(self._lin(self.time_in, t_freq, mode)), mode)
+        temb6 = self._lin(self.time_proj, F.silu(temb), mode).view(6, cfg.dim)
+        ctx = self._lin(self.text_hidden, self._lin(self.text_in, text, mode, gelu=True), mode)
+        return temb.view(cfg.dim), temb6, ctx
+
+    def _embed(self, latent: torch.Tensor, t: float, text: torch.Tensor, mode: str):
+        cfg = self.cfg
+        pt, ph, pw = cfg.patch
+        C, Fr, H, W = latent.shape
+        grid = (Fr // pt, H // ph, W // pw)
+        x = F.conv3d(latent.unsqueeze(0), self.patch_w, self.patch_b, stride=cfg.patch)
+        x = x.flatten(2).squeeze(0).t().contiguous()                  # [L, dim]
+        cos, sin = rope_tables(cfg, grid, self.device)
+        temb, temb6, ctx = self._conditions(t, text, mode)
+        return x, cos, sin, temb, temb6, ctx, grid
+
+    def _head(self, x: torch.Tensor, temb: torch.Tensor, mode: str) -> torch.Tensor:
+        cfg = self.cfg
+        shift, scale = (m.contiguous() for m in (self.out_table + temb.float()))
+        if mode == "nvfp4":
+            return self.proj_out.nvfp4(FP4Tensor.from_norm_mod(x, scale=scale, shift=shift, eps=cfg.eps))
+        return self.proj_out.dequant((layer_norm(x, cfg.eps) * (1 + scale) + shift).to(x.dtype),
+                                     reorder=mode == "dequant_reordered")
+
+    def _unpatchify(self, y: torch.Tensor, grid) -> torch.Tensor:
+        cfg = self.cfg
+        pt, ph, pw = cfg.patch
+        f, h, w = grid
+        y = y.reshape(f, h, w, pt, ph, pw, cfg.out_channels).permute(6, 0, 3, 1, 4, 2, 5)
+        return y.reshape(cfg.out_channels, f * pt, h * ph, w * pw)
+
+    def forward(self, latent: torch.Tensor, t: float, text: torch.Tensor, mode: str = "nvfp4",
+                group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+        """latent ``[C, F, H, W]`` bf16, text ``[512, 4096]`` bf16 -> ``[C_out, F, H, W]``.
+        With ``group`` each rank processes its contiguous shard of the token sequence and
+        returns the full output (gathered) on every rank."""
+        x, cos, sin, temb, temb6, ctx, grid = self._embed(latent, t, text, mode)
+        L = x.shape[0]
+        P = dist.get_world_size(group) if group is not None else 1
+        if P > 1:
+            if L % P != 0:
+                raise ValueError(f"tokens ({L}) must divide by the world size ({P})")
+            r = dist.get_rank(group)
+            sl = slice(r * (L // P), (r + 1) * (L // P))
+            x, cos, sin = x[sl].contiguous(), cos[sl], sin[sl]
+        for blk in self.blocks:
+            x = blk.forward(x, ctx, temb6, cos, sin, mode, group if P > 1 else None)
+        y = self._head(x, temb, mode)
+        if P > 1:
+            parts = [torch.empty_like(y) for _ in range(P)]
+            dist.all_gather(parts, y.contiguous(), group=group)
+            y = torch.cat(parts, dim=0)
+        return self._unpatchify(y, grid)
+
+    def compare_blocks(self, latent: torch.Tensor, t: float, text: torch.Tensor
+                       ) -> List[Tuple[float, float]]:
+        """Every block evaluated both ways FROM THE SAME INPUT (the NVFP4 trajectory's): per
+        block ``(cosine of the outputs, cosine of the block's own contribution out - in)``.
+        This is the per-block statement of parity; the free-running step comparison on top of
+        it also measures how fast FP4 re-quantization amplifies last-bit differences."""
+        x, cos, sin, temb, temb6, ctx, grid = self._embed(latent, t, text, "nvfp4")
+        out = []
+        for blk in self.blocks:
+            y = blk.forward(x, ctx, temb6, cos, sin, "nvfp4")
+            ref = blk.forward(x, ctx, temb6, cos, sin, "dequant")
+            out.append((_cosine(y, ref), _cosine(y.float() - x.float(), ref.float() - x.float())))
+            x = y
+        return out
+
+    def linear_flops(self, tokens: int, text_tokens: int = 512) -> float:
+        cfg = self.cfg
+        d = cfg.dim
+        per_block = 2 * tokens * (3 * d * d + d * d + d * d + d * d + 2 * cfg.ffn * d) \
+            + 2 * text_tokens * 2 * d * d
+        return per_block * len(self.blocks)
+
+    def attention_flops(self, tokens: int, text_tokens: int = 512) -> float:
+        cfg = self.cfg
+        return len(self.blocks) * 4 * cfg.dim * tokens * (tokens + text_tokens)

@@ -1,0 +1,150 @@
+"""DiT step latency on the NVFP4 path: ``python -m blackwell_diffusion_rtx6000_5090_i2v_b200.dit_step``.
+
+One denoising step of the Wan 2.2 shaped model (``dit.WanDiT``; random weights, seeded
+synthetic latent and text) on one GPU, or token-sharded over the ranks of a ``torchrun``
+launch with the Ulysses exchange around self-attention.  Prints one JSON line: step latency
+(CUDA events, max over ranks), the per-component device time of rank 0, the linears'
+aggregate TFLOP/s, and -- with ``--check`` -- the cosine of the step output against the same
+model evaluated with dequantize-then-matmul linears (and, on several ranks, against the
+unsharded model run on rank 0).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+
+import torch
+import torch.distributed as dist
+
+from . import dit, nvfp4
+
+LATENTS = {"5b": (48, 31, 44, 80), "14b": (16, 21, 60, 104)}   # -> 27280 / 32760 tokens
+CONFIGS = {"5b": dit.WAN22_TI2V_5B, "14b": dit.WAN22_A14B}
+
+
+def _cos(a: torch.Tensor, b: torch.Tensor) -> float:
+    a, b = a.double().flatten(), b.double().flatten()
+    return float(torch.dot(a, b) / (a.norm() * b.norm()))
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("--config", choices=sorted(CONFIGS), default="5b")
+    ap.add_argument("--layers", type=int, default=None, help="blocks to build (default: all)")
+    ap.add_argument("--frames", type=int, default=None, help="latent frames (default: the config's)")
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=1)
+    ap.add_argument("--check", action="store_true", help="cosine against the dequant model")
+    ap.add_argument("--sdpa", choices=["default", "flash", "cudnn"], default="default")
+    args = ap.parse_args(argv)
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        group = dist.group.WORLD
+    nvfp4.init()
+
+    cfg = CONFIGS[args.config]
+    C, Fr, H, W = LATENTS[args.config]
+    if args.frames:
+        Fr = args.frames
+    model = dit.WanDiT(cfg, device=f"cuda:{local}", seed=1234 + (3 if args.config == "5b" else 4),
+                       layers=args.layers)
+    g = torch.Generator(device="cuda").manual_seed(4321)
+    latent = torch.randn(C, Fr, H, W, generator=g, device="cuda").to(torch.bfloat16)
+    text = torch.randn(512, cfg.text_dim, generator=g, device="cuda").to(torch.bfloat16)
+    tokens = Fr * (H // 2) * (W // 2)
+
+    backends = None
+    if args.sdpa != "default":
+        from torch.nn.attention import SDPBackend
+        backends = [SDPBackend.FLASH_ATTENTION if args.sdpa == "flash" else SDPBackend.CUDNN_ATTENTION]
+
+    def step(mode="nvfp4", grp=group):
+        if backends is not None:
+            from torch.nn.attention import sdpa_kernel
+            with sdpa_kernel(backends):
+                return model.forward(latent, 500.0, text, mode=mode, group=grp)
+        return model.forward(latent, 500.0, text, mode=mode, group=grp)
+
+    def fence():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.no_grad():
+        for _ in range(args.warmup):
+            y = step()
+        times = []
+        for _ in range(args.steps):
+            fence()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            y = step()
+            e1.record()
+            fence()
+            t = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            times.append(float(t))
+        nvfp4.check_status()
+        # one more step with the per-component marks on
+        dit.TIMELINE = dit.Timeline()
+        dit.TIMELINE.mark("start")
+        step()
+        dit.TIMELINE.mark("other")
+        parts = dit.TIMELINE.totals_ms()
+        dit.TIMELINE = None
+
+        checks = {}
+        if args.check:
+            ref = step(mode="dequant")
+            checks["cosine_vs_dequant_model"] = _cos(y, ref)
+            # control: the dequant model against itself with every GEMM's K sum in reverse order
+            ctl = step(mode="dequant_reordered")
+            checks["cosine_dequant_model_vs_itself_reordered_sums"] = _cos(ref, ctl)
+            del ctl
+            if world == 1:
+                per_block = model.compare_blocks(latent, 500.0, text)
+                checks["per_block_same_input_cosine_min"] = min(c for c, _ in per_block)
+                checks["per_block_same_input_delta_cosine_min"] = min(d for _, d in per_block)
+            if world > 1:
+                fence()
+                if rank == 0:
+                    full = step(grp=None)
+                    checks["cosine_sharded_vs_single_gpu"] = _cos(y, full)
+                fence()
+
+    if rank == 0:
+        ms = statistics.median(times)
+        lin = model.linear_flops(tokens)
+        att = model.attention_flops(tokens)
+        gemm_ms = parts.get("gemm", 0.0) + parts.get("text_kv", 0.0)
+        line = {
+            "metric": "dit_step_latency", "unit": "ms", "value": round(ms, 3),
+            "higher_is_better": False, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "config": {"workload": f"wan2.2 {args.config} shape, {len(model.blocks)} blocks, "
+                                   f"{tokens} tokens, text 512x{cfg.text_dim}",
+                       "tokens_per_rank": tokens // world, "sdpa": args.sdpa,
+                       "parallelism": f"ulysses{world}" if world > 1 else "single"},
+            "all_ms": [round(t, 3) for t in times],
+            "components_ms_rank0": {k: round(v, 3) for k, v in sorted(parts.items())},
+            "linear_tflop": round(lin / 1e12, 2), "attention_tflop": round(att / 1e12, 2),
+            "gemm_tflops_per_gpu": round(lin / world / (gemm_ms * 1e-3) / 1e12, 1) if gemm_ms else None,
+            "data": "synthetic", "dtype": "nvfp4 linears, bf16 attention",
+        }
+        line.update(checks)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -81,7 +81,10 @@ class FP4Tensor:
     @staticmethod
     def from_bfloat16(input: torch.Tensor,
                       mode: QuantizationMode = QuantizationMode.block_1d,
-                      *, linear_scales: bool = True, swizzled_scales: bool = True) -> "FP4Tensor":
+                      *, linear_scales: bool = True, swizzled_scales: bool = True,
+                      amax: Optional[torch.Tensor] = None) -> "FP4Tensor":
+        """``amax`` (additive): a one-element fp32 device tensor already holding max|input|,
+        e.g. from the GEMM that produced ``input``; the amax pass is then skipped."""
         if input.dtype != torch.bfloat16:
             raise RuntimeError("[s4] [nvfp4] [tensor] Input must be BFloat16")
         if not input.is_cuda:
@@ -107,7 +110,12 @@ class FP4Tensor:
                 rows, cols = (1, n_pad) if n_pad else (0, 0)
             self._rows, self._cols = rows, cols
             dev = input.device
-            self._amax = torch.empty(1, dtype=torch.float32, device=dev)
+            if amax is not None and (amax.dtype != torch.float32 or amax.numel() != 1
+                                     or amax.device != dev):
+                raise RuntimeError("[s4] [nvfp4] [tensor] amax must be a one-element float32 "
+                                   "tensor on the input's device")
+            self._amax = amax if amax is not None else torch.empty(1, dtype=torch.float32,
+                                                                   device=dev)
             self._gscale = torch.empty(1, dtype=torch.float32, device=dev)
             self._data = torch.empty(rows * cols // 2, dtype=torch.uint8, device=dev)
             self._scales = (torch.empty(rows * cols // FP4_BLOCK_SIZE, dtype=torch.uint8, device=dev)
@@ -116,8 +124,9 @@ class FP4Tensor:
                                             dtype=torch.uint8, device=dev)
                                 if swizzled_scales and rows * cols > 0 else None)
             st = N.stream_ptr()
-            N.check(N.lib.nvfp4_amax_bf16(N.ptr(x), rows * cols, N.ptr(self._amax), st),
-                    "[tensor] amax")
+            if amax is None:
+                N.check(N.lib.nvfp4_amax_bf16(N.ptr(x), rows * cols, N.ptr(self._amax), st),
+                        "[tensor] amax")
             N.check(N.lib.nvfp4_quantize_bf16(N.ptr(x), rows, cols, N.ptr(self._amax),
                                               N.ptr(self._data), N.ptr(self._scales),
                                               N.ptr(self._scales_swz), N.ptr(self._gscale), st),
