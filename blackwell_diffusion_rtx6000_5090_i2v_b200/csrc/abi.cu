@@ -22,6 +22,19 @@ int check_device_sm100() {
   return major == 10 ? NVFP4_OK : NVFP4_ERR_UNSUPPORTED_ARCH;
 }
 
+int sm_count() {
+  static int cached[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (cached[dev] == 0) {
+    int n = 0;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    cached[dev] = n > 0 ? n : 148;
+  }
+  return cached[dev];
+}
+
 }  // namespace nvfp4
 
 extern "C" {

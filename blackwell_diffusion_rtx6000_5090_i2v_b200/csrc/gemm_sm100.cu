@@ -657,19 +657,6 @@ static bool make_d_map(CUtensorMap* map, void* base, int64_t M, int64_t N) {
             CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-static int sm_count() {
-  static int cached[64];
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) dev = 0;
-  if (cached[dev] == 0) {
-    int n = 0;
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    cached[dev] = n > 0 ? n : 148;
-  }
-  return cached[dev];
-}
-
 }  // namespace gemm
 }  // namespace nvfp4
 
@@ -739,7 +726,7 @@ extern "C" int nvfp4_gemm(const uint8_t* a_packed, const uint8_t* b_packed,
     return NVFP4_ERR_LAUNCH_FAILED;
   // one CTA pair (cluster of two) per pair of SMs, each pair walking 256x256 tiles
   const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles;
-  const int max_pairs = gemm::sm_count() / 2;
+  const int max_pairs = sm_count() / 2;
   const unsigned pairs = (unsigned)(tiles < max_pairs ? tiles : max_pairs);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs, 1, 1);

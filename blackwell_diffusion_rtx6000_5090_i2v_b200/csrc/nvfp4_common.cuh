@@ -91,5 +91,6 @@ __device__ __forceinline__ float bf16hi_to_f32(uint32_t w) {
 // Host helpers shared by the entry points.
 int check_device_sm100();                 // NVFP4_OK or NVFP4_ERR_UNSUPPORTED_ARCH (cached per device)
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+int sm_count();                           // SMs of the current device (cached per device)
 
 }  // namespace nvfp4

@@ -178,16 +178,17 @@ class FP4Tensor:
             stats = torch.empty(rows, 2, dtype=torch.float32, device=dev)
             normed = torch.empty_like(xc) if return_normed else None
             st = N.stream_ptr()
+            status = N.ptr(N.status_word(dev))
             w_, b_, sc_, sh_ = (N.ptr(v) for v in vecs)
             N.check(N.lib.nvfp4_norm_mod_amax_bf16(N.ptr(xc), rows, cols, w_, b_, sc_, sh_,
                                                    1 if rms else 0, float(eps), N.ptr(stats),
-                                                   N.ptr(self._amax), N.ptr(normed), st),
+                                                   N.ptr(self._amax), N.ptr(normed), status, st),
                     "[tensor] norm+amax")
             N.check(N.lib.nvfp4_norm_mod_quantize_bf16(N.ptr(xc), rows, cols, w_, b_, sc_, sh_,
                                                        N.ptr(stats), N.ptr(self._amax),
                                                        N.ptr(self._data), N.ptr(self._scales),
                                                        N.ptr(self._scales_swz),
-                                                       N.ptr(self._gscale), st),
+                                                       N.ptr(self._gscale), status, st),
                     "[tensor] norm+quantize")
         return (self, normed) if return_normed else self
 

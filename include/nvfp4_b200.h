@@ -131,18 +131,21 @@ NVFP4_API int nvfp4_gemm(const uint8_t* a_packed, const uint8_t* b_packed, const
  *   sweep 2 (nvfp4_norm_mod_quantize_bf16): recomputes the result from x and row_stats and
  *     writes packed nibbles, scales (linear and/or swizzled, either nullable) and the FP32
  *     tensor scale, exactly as nvfp4_quantize_bf16 would from the bf16 result.
- * cols % 16 == 0 and cols <= 16384. */
+ * cols % 16 == 0 and cols <= 16384.  Rows reach the SMs as bulk copies into shared memory;
+ * a copy that does not arrive within about two seconds makes the kernel give up and store
+ * 0x900 in *status_dev (nullable; the caller zeroes it once and may poll it at any time). */
 NVFP4_API int nvfp4_norm_mod_amax_bf16(const void* x_bf16, int64_t rows, int64_t cols,
                                        const float* weight, const float* bias, const float* scale,
                                        const float* shift, int rms, float eps, float* row_stats,
-                                       float* amax_dev, void* h_out_bf16, void* stream);
+                                       float* amax_dev, void* h_out_bf16, int* status_dev,
+                                       void* stream);
 NVFP4_API int nvfp4_norm_mod_quantize_bf16(const void* x_bf16, int64_t rows, int64_t cols,
                                            const float* weight, const float* bias,
                                            const float* scale, const float* shift,
                                            const float* row_stats, const float* amax_dev,
                                            uint8_t* packed, uint8_t* scales_linear,
                                            uint8_t* scales_swizzled, float* global_scale_dev,
-                                           void* stream);
+                                           int* status_dev, void* stream);
 
 /* Has no counterpart in the reference.  One whole linear, y = act(x W^T + bias), for
  * callers that cannot allocate device memory (code inside a region where cudaMalloc is not
