@@ -40,6 +40,8 @@ SIGNATURES = {
     "nvfp4_norm_mod_amax_bf16": (_i, [_p, _i64, _i64, _p, _p, _p, _p, _i, _f, _p, _p, _p, _p, _p]),
     "nvfp4_norm_mod_quantize_bf16": (_i, [_p, _i64, _i64, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p,
                                           _p, _p]),
+    "nvfp4_qk_norm_rope_bf16": (_i, [_p, _p, _p, _i64, _i64, _i, _i, _p, _p, _f, _p, _p, _p, _p,
+                                     _i64, _i64, _p, _p]),
     "nvfp4_linear_bf16_static": (_i, [_p, _i64, _i64, _p, _p, _p, _i64, _p, _i, _p, _p, _p]),
     "nvfp4_linear_bf16_static_max_elements": (_i64, []),
 }

@@ -46,6 +46,17 @@ __device__ __forceinline__ float global_encode_scale(float amax) {
   return s;
 }
 
+// x / 6 for finite x >= 0, bit-identical to the IEEE quotient: one multiply by fl(1/6) and one
+// residual correction (two FMAs).  The residual of a tiny quotient is itself inexact, so very
+// small x takes the division.  Checked against x / 6.0f for every bf16 x >= 1e-30 and two
+// million fp32 values.
+__device__ __forceinline__ float div_by_6(float x) {
+  const float c = 0x1.555556p-3f;
+  const float q0 = __fmul_rn(x, c);
+  const float q = __fmaf_rn(__fmaf_rn(-6.0f, q0, x), c, q0);
+  return x < 1e-30f ? __fdiv_rn(x, 6.0f) : q;
+}
+
 // E4M3 block scale: rn_satfinite( min( (amax_b / 6) * S_enc, FLT_MAX ) ).
 __device__ __forceinline__ uint8_t block_scale_e4m3(float amax_b, float s_enc) {
   float d = __fmul_rn(__fdiv_rn(amax_b, 6.0f), s_enc);
@@ -84,6 +95,53 @@ __device__ __forceinline__ uint32_t f32x8_to_e2m1x8(float v0, float v1, float v2
 __device__ __forceinline__ float bf16lo_to_f32(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16hi_to_f32(uint32_t w) {
   return __uint_as_float(w & 0xFFFF0000u);
+}
+
+// Two fp32 lanes per instruction (sm_100): each lane is rounded exactly like the scalar
+// op, the pair costs one issue slot.
+__device__ __forceinline__ float2 f2_add(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "add.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 f2_sub(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "sub.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 f2_mul(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "mul.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 f2_fma(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "mov.b64 rc, {%6, %7};\n\tfma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 bf16x2_to_f2(uint32_t w) {
+  return make_float2(bf16lo_to_f32(w), bf16hi_to_f32(w));
+}
+// (lo, hi) -> packed bf16x2, round to nearest even: one instruction for the pair
+__device__ __forceinline__ uint32_t f2_to_bf16x2(float2 v) {
+  uint32_t d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(v.y), "f"(v.x));
+  return d;
+}
+// max(acc, |v|) per bf16 lane (inputs finite)
+__device__ __forceinline__ uint32_t bf16x2_max_abs(uint32_t acc, uint32_t v) {
+  uint32_t d;
+  asm("{\n\t.reg .b32 t;\n\tabs.bf16x2 t, %2;\n\tmax.bf16x2 %0, %1, t;\n\t}"
+      : "=r"(d) : "r"(acc), "r"(v));
+  return d;
 }
 
 #endif  // __CUDACC__

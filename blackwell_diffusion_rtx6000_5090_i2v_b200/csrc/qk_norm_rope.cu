@@ -1,0 +1,334 @@
+// q/k RMSNorm across heads + rotary embedding, one pass over the QKV GEMM's output.
+//
+//   n = bf16( (x * rsqrt(mean(x^2) + eps)) * gain )            per token, over all heads
+//   o[2i]   = bf16( n[2i] * c_i - n[2i+1] * s_i )              per head, pair i of head_dim/2
+//   o[2i+1] = bf16( n[2i] * s_i + n[2i+1] * c_i )
+//
+// which is what the DiT block does between its QKV linear and attention
+// (fx/src/s4/models/wan22/wan_transformer.py:91-92,114-115 for the norms, :61-75 for the
+// rotation), there as about twenty elementwise torch kernels with fp32 round trips.  Every
+// product and sum is rounded separately in fp32, as the unfused ops round them.  The value
+// tensor can be carried along untouched so that q, k and v land in one packed
+// [tokens, heads, 3 * head_dim] buffer ready for a head/sequence exchange.
+//
+// Layout of the work is that of the fused norm + quantize kernel: a thread owns the same 16
+// columns of every row (its gains stay in registers), a CTA walks over groups of kR tokens
+// that bulk copies stage in a ring of shared-memory slots, one CTA-wide reduction per group.
+// blockIdx.y selects the tensor: 0 = q, 1 = k, 2 = v (copy only).
+#include "nvfp4_common.cuh"
+
+namespace nvfp4 {
+namespace {
+
+constexpr int kMaxThreads = 512;
+constexpr int kMaxWarps = kMaxThreads / 32;
+constexpr int kStages = 3;
+constexpr int kR = 2;                              // tokens per group
+constexpr long long kWaitCycles = 4000000000LL;    // about two seconds; then give up
+constexpr int kErrCopyTimeout = 0xA00;             // status code: a token group never arrived
+
+struct RopeArgs {
+  const uint8_t* in[3];        // q, k, v: first element of row 0 (v may be null)
+  int64_t in_row_bytes;        // distance between rows of an input
+  int64_t rows;
+  int dim;                     // heads * head_dim
+  int head_dim;
+  const float* gain[2];        // nullable: unit gain
+  float eps;
+  const float2* cos_sin;       // [rows][head_dim / 2] (cos of pair i, sin of pair i)
+  uint8_t* out[3];
+  int64_t out_row_bytes;
+  int64_t out_head_bytes;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Contiguous global -> this CTA's shared memory, bytes reported to `bar`.  One destination,
+// nothing broadcast.  Addresses 16-byte aligned, size a multiple of 16.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+// Bounded wait; on expiry the CTA carries on without the data (all barriers are still
+// reached by all threads) and the status word says that its output is meaningless.
+__device__ __forceinline__ void wait_group(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                           int* status) {
+  if (mbar_try_wait(bar, parity)) return;
+  const long long t0 = clock64();
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try_wait(bar, parity)) return;
+    if ((it & 255u) == 0) {
+      if (*abort_flag) return;
+      if (clock64() - t0 > kWaitCycles) {
+        *abort_flag = 1;
+        if (status) atomicCAS(status, 0, kErrCopyTimeout);
+        return;
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kMaxThreads)
+qk_norm_rope_kernel(const RopeArgs p) {
+  extern __shared__ __align__(128) uint8_t ring[];          // kStages slots of kR rows
+  __shared__ __align__(16) float red[2][kR][kMaxWarps];
+  __shared__ __align__(8) uint64_t full[kStages];
+  __shared__ int abort_flag;
+  const int which = blockIdx.y;                             // 0 q, 1 k, 2 v
+  const int T = blockDim.x;
+  const int warps = T >> 5;
+  const int units = p.dim >> 4;                             // 16-element pieces per row
+  const uint32_t row_bytes = (uint32_t)p.dim * 2u;
+  const uint32_t slot_bytes = row_bytes * kR;
+  const int64_t groups = (p.rows + kR - 1) / kR;
+  const uint8_t* in = which == 0 ? p.in[0] : (which == 1 ? p.in[1] : p.in[2]);
+  uint8_t* out = which == 0 ? p.out[0] : (which == 1 ? p.out[1] : p.out[2]);
+  const float* gain_ptr = which == 0 ? p.gain[0] : (which == 1 ? p.gain[1] : nullptr);
+
+  auto issue = [&](int64_t g, int slot) {
+    const int64_t base = g * kR;
+    const int n = (int)(p.rows - base < kR ? p.rows - base : kR);
+    const uint32_t bar = smem_u32(&full[slot]);
+    mbar_expect_tx(bar, (uint32_t)n * row_bytes);
+    for (int r = 0; r < n; ++r)
+      bulk_load(smem_u32(ring + (size_t)slot * slot_bytes + (size_t)r * row_bytes),
+                in + (base + r) * p.in_row_bytes, row_bytes, bar);
+  };
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+#pragma unroll
+    for (int s = 0; s < kStages; ++s) mbar_init(smem_u32(&full[s]), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  for (int i = threadIdx.x; i < 2 * kR * kMaxWarps; i += T) (&red[0][0][0])[i] = 0.0f;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int s = 0; s < kStages; ++s) {
+      const int64_t g = (int64_t)blockIdx.x + (int64_t)s * gridDim.x;
+      if (g < groups) issue(g, s);
+    }
+  }
+
+  // this thread's 16 columns: head, offset in the head, gains
+  const int u = threadIdx.x;
+  const bool live = u < units;
+  const int col = live ? u * 16 : 0;
+  const int head = col / p.head_dim;
+  const int d0 = col - head * p.head_dim;
+  const int64_t out_off = (int64_t)head * p.out_head_bytes + (int64_t)d0 * 2;
+  float2 gain[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) gain[e] = make_float2(1.0f, 1.0f);
+  if (gain_ptr) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float4 a = __ldg(reinterpret_cast<const float4*>(gain_ptr + col) + q);
+      gain[2 * q] = make_float2(a.x, a.y);
+      gain[2 * q + 1] = make_float2(a.z, a.w);
+    }
+  }
+  const float dim_f = (float)p.dim;
+  const int half_hd = p.head_dim >> 1;
+
+  int slot = 0;
+  uint32_t phase = 0;
+  int parity = 0;
+  for (int64_t g = blockIdx.x; g < groups; g += gridDim.x, parity ^= 1) {
+    const int64_t base = g * kR;
+    // this group's rotation table entries: asked for before the wait, used after the reduction
+    float4 cs[kR][4];
+    const bool rotate = which < 2 && p.cos_sin != nullptr;
+    if (rotate) {
+#pragma unroll
+      for (int r = 0; r < kR; ++r) {
+        const int64_t row = base + r < p.rows ? base + r : base;
+        const float4* t = reinterpret_cast<const float4*>(p.cos_sin + row * half_hd + (d0 >> 1));
+#pragma unroll
+        for (int q = 0; q < 4; ++q) cs[r][q] = __ldg(t + q);
+      }
+    }
+    wait_group(smem_u32(&full[slot]), phase, &abort_flag, p.status);
+    const uint8_t* slot_ptr = ring + (size_t)slot * slot_bytes;
+    uint32_t xp[kR][8];
+    bool row_ok[kR];
+#pragma unroll
+    for (int r = 0; r < kR; ++r) {
+      row_ok[r] = base + r < p.rows;
+      const uint4* src = reinterpret_cast<const uint4*>(slot_ptr + (size_t)r * row_bytes) + 2 * (col >> 4);
+      const uint4 a = src[0], b = src[1];
+      xp[r][0] = a.x; xp[r][1] = a.y; xp[r][2] = a.z; xp[r][3] = a.w;
+      xp[r][4] = b.x; xp[r][5] = b.y; xp[r][6] = b.z; xp[r][7] = b.w;
+    }
+    float rstd[kR];
+    if (which < 2) {
+      float acc[kR];
+#pragma unroll
+      for (int r = 0; r < kR; ++r) {
+        float2 s2 = make_float2(0.0f, 0.0f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float2 x = bf16x2_to_f2(xp[r][e]);
+          s2 = f2_fma(x, x, s2);
+        }
+        acc[r] = (live && row_ok[r]) ? s2.x + s2.y : 0.0f;
+      }
+      // warp stage: fold the two values across lane bit 4, finish over the other bits
+      {
+        static_assert(kR == 2, "the fold below is written for two rows per group");
+        const int lane = threadIdx.x & 31;
+        const bool up = (lane & 16) != 0;
+        const float keep = up ? acc[1] : acc[0], give = up ? acc[0] : acc[1];
+        float v = keep + __shfl_xor_sync(0xffffffffu, give, 16);
+        v += __shfl_xor_sync(0xffffffffu, v, 8);
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        if ((lane & 15) == 0) red[parity][up ? 1 : 0][threadIdx.x >> 5] = v;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int r = 0; r < kR; ++r) {
+        float t = 0.0f;
+        for (int w4 = 0; w4 < warps; w4 += 4) {
+          const float4 q = *reinterpret_cast<const float4*>(&red[parity][r][w4]);
+          t += (q.x + q.y) + (q.z + q.w);
+        }
+        rstd[r] = rsqrtf(t / dim_f + p.eps);
+      }
+    } else {
+      __syncthreads();
+    }
+    // every thread holds its piece: the slot can take the group kStages ahead
+    {
+      const int64_t gn = g + (int64_t)kStages * gridDim.x;
+      if (threadIdx.x == 0 && gn < groups) issue(gn, slot);
+    }
+
+#pragma unroll
+    for (int r = 0; r < kR; ++r) {
+      if (!(live && row_ok[r])) continue;
+      uint32_t o[8];
+      if (which < 2) {
+        const float2 r2 = make_float2(rstd[r], rstd[r]);
+        const float2 sign = make_float2(-1.0f, 1.0f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          // normalized pair, rounded to bf16 as the unfused model rounds it
+          const uint32_t nb = f2_to_bf16x2(f2_mul(f2_mul(bf16x2_to_f2(xp[r][e]), r2), gain[e]));
+          if (!rotate) {
+            o[e] = nb;
+            continue;
+          }
+          const float2 n = bf16x2_to_f2(nb);
+          const float4 t4 = cs[r][e >> 1];
+          const float c = (e & 1) ? t4.z : t4.x, s = (e & 1) ? t4.w : t4.y;
+          const float2 nc = f2_mul(n, make_float2(c, c));                      // (x1 c, x2 c)
+          const float2 ns = f2_mul(make_float2(n.y, n.x), make_float2(s, s));  // (x2 s, x1 s)
+          o[e] = f2_to_bf16x2(f2_fma(ns, sign, nc));     // (x1 c - x2 s, x2 c + x1 s), +-1 exact
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = xp[r][e];
+      }
+      uint4* dst = reinterpret_cast<uint4*>(out + (base + r) * p.out_row_bytes + out_off);
+      dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+      dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+    if (++slot == kStages) {
+      slot = 0;
+      phase ^= 1u;
+    }
+  }
+  if (abort_flag) {
+    // a wait expired: give copies still in flight time to land before the shared memory is
+    // handed to another CTA
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) {
+    }
+  }
+}
+
+}  // namespace
+}  // namespace nvfp4
+
+using namespace nvfp4;
+
+extern "C" NVFP4_API int nvfp4_qk_norm_rope_bf16(const void* q_in, const void* k_in, const void* v_in,
+                                       int64_t in_row_stride, int64_t rows, int heads, int head_dim,
+                                       const float* gain_q, const float* gain_k, float eps,
+                                       const float* cos_sin, void* q_out, void* k_out, void* v_out,
+                                       int64_t out_row_stride, int64_t out_head_stride,
+                                       int* status_dev, void* stream) {
+  const int64_t dim = (int64_t)heads * head_dim;
+  if (rows < 0 || heads <= 0 || head_dim <= 0 || head_dim % 16 != 0 || dim > 16 * kMaxThreads ||
+      in_row_stride < dim || out_head_stride < head_dim || in_row_stride % 8 != 0 ||
+      out_row_stride % 8 != 0 || out_head_stride % 8 != 0)
+    return NVFP4_ERR_BAD_ARG;
+  if (rows > 0 && (!q_in || !q_out)) return NVFP4_ERR_BAD_ARG;
+  if ((k_in == nullptr) != (k_out == nullptr) || (v_in == nullptr) != (v_out == nullptr) ||
+      (v_in && !k_in))
+    return NVFP4_ERR_BAD_ARG;
+  if (!aligned16(q_in) || !aligned16(k_in) || !aligned16(v_in) || !aligned16(q_out) ||
+      !aligned16(k_out) || !aligned16(v_out) || !aligned16(gain_q) || !aligned16(gain_k) ||
+      !aligned16(cos_sin))
+    return NVFP4_ERR_BAD_ALIGN;
+  int rc = check_device_sm100();
+  if (rc != NVFP4_OK) return rc;
+  if (rows == 0) return NVFP4_OK;
+  RopeArgs a{};
+  a.in[0] = static_cast<const uint8_t*>(q_in);
+  a.in[1] = static_cast<const uint8_t*>(k_in);
+  a.in[2] = static_cast<const uint8_t*>(v_in);
+  a.in_row_bytes = in_row_stride * 2;
+  a.rows = rows;
+  a.dim = (int)dim;
+  a.head_dim = head_dim;
+  a.gain[0] = gain_q;
+  a.gain[1] = gain_k;
+  a.eps = eps;
+  a.cos_sin = reinterpret_cast<const float2*>(cos_sin);
+  a.out[0] = static_cast<uint8_t*>(q_out);
+  a.out[1] = static_cast<uint8_t*>(k_out);
+  a.out[2] = static_cast<uint8_t*>(v_out);
+  a.out_row_bytes = out_row_stride * 2;
+  a.out_head_bytes = out_head_stride * 2;
+  a.status = status_dev;
+  const int threads = (int)((dim / 16 + 31) / 32 * 32);
+  const size_t smem = (size_t)kStages * kR * dim * 2;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (cudaFuncSetAttribute(qk_norm_rope_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (int)smem) != cudaSuccess)
+    return NVFP4_ERR_LAUNCH_FAILED;
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, qk_norm_rope_kernel, threads, smem) !=
+          cudaSuccess || per_sm < 1)
+    return NVFP4_ERR_LAUNCH_FAILED;
+  const int tensors = v_in ? 3 : (k_in ? 2 : 1);
+  const int64_t groups = (rows + kR - 1) / kR;
+  int64_t gx = ((int64_t)sm_count() * per_sm + tensors - 1) / tensors;
+  if (gx > groups) gx = groups;
+  if (gx < 1) gx = 1;
+  qk_norm_rope_kernel<<<dim3((unsigned)gx, (unsigned)tensors), threads, smem, st>>>(a);
+  return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_ERR_LAUNCH_FAILED;
+}

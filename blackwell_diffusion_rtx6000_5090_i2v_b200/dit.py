@@ -35,6 +35,7 @@ import torch
 import torch.distributed as dist
 import torch.nn.functional as F
 
+from . import _native as N
 from . import ulysses
 from .nvfp4 import FP4Tensor, fp4_gemm
 
@@ -193,6 +194,62 @@ def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.T
     return out.to(x.dtype)
 
 
+def pack_rope_table(cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """``[L, D]`` cos / sin tables -> fp32 ``[L, D/2, 2]`` holding, for each rotated pair, the
+    two entries :func:`apply_rope` uses (``cos[:, 0::2]`` and ``sin[:, 1::2]``)."""
+    return torch.stack([cos[:, 0::2], sin[:, 1::2]], dim=-1).contiguous()
+
+
+def qk_norm_rope(qkv: torch.Tensor, heads: int, head_dim: int, gain_q: Optional[torch.Tensor],
+                 gain_k: Optional[torch.Tensor], eps: float, cos_sin: torch.Tensor,
+                 packed: bool = False):
+    """RMSNorm across heads of q and k, then the rotary embedding, in one kernel over the
+    ``[L, 3*dim]`` output of the QKV linear (the fused form of ``rms_norm`` + ``apply_rope``
+    below).  Returns ``(q, k, v)`` as ``[L, heads, head_dim]`` tensors -- v is a view of
+    ``qkv`` -- or, with ``packed``, one ``[L, heads, 3*head_dim]`` tensor holding q | k | v per
+    head, the layout the head/sequence exchange sends."""
+    L, three_dim = qkv.shape
+    dim = heads * head_dim
+    if three_dim != 3 * dim or qkv.dtype != torch.bfloat16 or not qkv.is_contiguous():
+        raise RuntimeError("qk_norm_rope: qkv must be a contiguous bf16 [L, 3*heads*head_dim] tensor")
+    if cos_sin.shape != (L, head_dim // 2, 2) or cos_sin.dtype != torch.float32 or \
+            not cos_sin.is_contiguous():
+        raise RuntimeError("qk_norm_rope: cos_sin must be a contiguous fp32 [L, head_dim/2, 2] tensor")
+    base = qkv.data_ptr()
+    st = N.stream_ptr()
+    status = N.ptr(N.status_word(qkv.device))
+    if packed:
+        out = torch.empty(L, heads, 3 * head_dim, dtype=torch.bfloat16, device=qkv.device)
+        o = out.data_ptr()
+        N.check(N.lib.nvfp4_qk_norm_rope_bf16(base, base + 2 * dim, base + 4 * dim, 3 * dim, L, heads,
+                                              head_dim, N.ptr(gain_q), N.ptr(gain_k), float(eps),
+                                              N.ptr(cos_sin), o, o + 2 * head_dim, o + 4 * head_dim,
+                                              3 * dim, 3 * head_dim, status, st), "qk_norm_rope")
+        return out
+    q = torch.empty(L, heads, head_dim, dtype=torch.bfloat16, device=qkv.device)
+    k = torch.empty_like(q)
+    N.check(N.lib.nvfp4_qk_norm_rope_bf16(base, base + 2 * dim, None, 3 * dim, L, heads, head_dim,
+                                          N.ptr(gain_q), N.ptr(gain_k), float(eps), N.ptr(cos_sin),
+                                          q.data_ptr(), k.data_ptr(), None, dim, head_dim, status, st),
+            "qk_norm_rope")
+    return q, k, qkv[:, 2 * dim:].view(L, heads, head_dim)
+
+
+def rms_norm_fused(x: torch.Tensor, heads: int, head_dim: int, gain: Optional[torch.Tensor],
+                   eps: float) -> torch.Tensor:
+    """RMSNorm over the last axis of a contiguous bf16 ``[L, heads*head_dim]`` tensor with the
+    same kernel (no rotation); returns ``[L, heads, head_dim]``."""
+    L, dim = x.shape
+    if dim != heads * head_dim or x.dtype != torch.bfloat16 or not x.is_contiguous():
+        raise RuntimeError("rms_norm_fused: x must be a contiguous bf16 [L, heads*head_dim] tensor")
+    out = torch.empty(L, heads, head_dim, dtype=torch.bfloat16, device=x.device)
+    N.check(N.lib.nvfp4_qk_norm_rope_bf16(x.data_ptr(), None, None, dim, L, heads, head_dim,
+                                          N.ptr(gain), None, float(eps), None, out.data_ptr(), None,
+                                          None, dim, head_dim, N.ptr(N.status_word(x.device)),
+                                          N.stream_ptr()), "rms_norm")
+    return out
+
+
 def rms_norm(x: torch.Tensor, gain: torch.Tensor, eps: float) -> torch.Tensor:
     xf = x.float()
     return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * gain).to(x.dtype)
@@ -227,6 +284,26 @@ class WanBlock:
         self._amax = torch.empty(1, dtype=torch.float32, device=device)
 
     # ---------------------------------------------------------------- parts --
+    def _self_attention_fused(self, qkv, cos_sin, group):
+        """nvfp4 path: one kernel between the QKV linear and attention (or the exchange)."""
+        cfg = self.cfg
+        L = qkv.shape[0]
+        if group is None:
+            q, k, v = qk_norm_rope(qkv, cfg.heads, cfg.head_dim, self.g_q, self.g_k, cfg.eps, cos_sin)
+            _mark("qk_norm_rope")
+        else:
+            packed = qk_norm_rope(qkv, cfg.heads, cfg.head_dim, self.g_q, self.g_k, cfg.eps, cos_sin,
+                                  packed=True)
+            _mark("qk_norm_rope")
+            q, k, v = ulysses.seq_to_heads(packed, group).split(cfg.head_dim, dim=-1)
+            _mark("exchange")
+        o = attention(q, k, v)
+        _mark("self_attention")
+        if group is not None:
+            o = ulysses.heads_to_seq(o.contiguous(), group)
+            _mark("exchange")
+        return o.reshape(L, cfg.dim)
+
     def _self_attention(self, q, k, v, cos, sin, group):
         cfg = self.cfg
         L = q.shape[0]
@@ -257,19 +334,20 @@ class WanBlock:
 
     # -------------------------------------------------------------- forward --
     def forward(self, x: torch.Tensor, ctx: torch.Tensor, temb6: torch.Tensor, cos, sin,
-                mode: str = "nvfp4", group=None) -> torch.Tensor:
+                mode: str = "nvfp4", group=None, cos_sin: Optional[torch.Tensor] = None) -> torch.Tensor:
         cfg = self.cfg
         mod = self.scale_shift_table + temb6.float()
         shift_msa, scale_msa, gate_msa, c_shift, c_scale, c_gate = (m.contiguous() for m in mod)
         L = x.shape[0]
         if mode == "nvfp4":
+            if cos_sin is None:
+                cos_sin = pack_rope_table(cos, sin)
             _mark("other")
             a = FP4Tensor.from_norm_mod(x, scale=scale_msa, shift=shift_msa, eps=cfg.eps)
             _mark("norm_quantize")
             qkv = self.qkv.nvfp4(a)
             _mark("gemm")
-            q, k, v = qkv.chunk(3, dim=-1)
-            o = self._self_attention(q, k, v, cos, sin, group)
+            o = self._self_attention_fused(qkv, cos_sin, group)
             oq = FP4Tensor.from_bfloat16(o.contiguous(), linear_scales=False)
             _mark("quantize")
             x = self.attn_out.nvfp4(oq, gate=gate_msa, C=x, beta=1.0)
@@ -278,7 +356,7 @@ class WanBlock:
             _mark("norm_quantize")
             q = self.cross_q.nvfp4(a)
             _mark("gemm")
-            q = rms_norm(q, self.g_cq, cfg.eps).view(L, cfg.heads, cfg.head_dim)
+            q = rms_norm_fused(q, cfg.heads, cfg.head_dim, self.g_cq, cfg.eps)
             _mark("qk_norm_rope")
             ck, cv = self._cross_kv(ctx, mode)
             _mark("text_kv")
@@ -332,6 +410,7 @@ class WanDiT:
         self.text_hidden = PackedLinear(d, d, gen, self.device)
         self.blocks: List[WanBlock] = [WanBlock(cfg, gen, self.device)
                                        for _ in range(layers if layers is not None else cfg.layers)]
+        self._rope: Dict[Tuple[int, int, int], Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = {}
         self.out_table = torch.randn(2, d, generator=gen, device=self.device) / d ** 0.5
         self.proj_out = PackedLinear(cfg.out_channels * pt * ph * pw, d, gen, self.device)
 
@@ -359,9 +438,12 @@ class WanDiT:
         grid = (Fr // pt, H // ph, W // pw)
         x = F.conv3d(latent.unsqueeze(0), self.patch_w, self.patch_b, stride=cfg.patch)
         x = x.flatten(2).squeeze(0).t().contiguous()                  # [L, dim]
-        cos, sin = rope_tables(cfg, grid, self.device)
+        if grid not in self._rope:          # tables depend on the grid only: built once
+            cos, sin = rope_tables(cfg, grid, self.device)
+            self._rope[grid] = (cos, sin, pack_rope_table(cos, sin))
+        cos, sin, cos_sin = self._rope[grid]
         temb, temb6, ctx = self._conditions(t, text, mode)
-        return x, cos, sin, temb, temb6, ctx, grid
+        return x, cos, sin, cos_sin, temb, temb6, ctx, grid
 
     def _head(self, x: torch.Tensor, temb: torch.Tensor, mode: str) -> torch.Tensor:
         cfg = self.cfg
@@ -383,7 +465,7 @@ class WanDiT:
         """latent ``[C, F, H, W]`` bf16, text ``[512, 4096]`` bf16 -> ``[C_out, F, H, W]``.
         With ``group`` each rank processes its contiguous shard of the token sequence and
         returns the full output (gathered) on every rank."""
-        x, cos, sin, temb, temb6, ctx, grid = self._embed(latent, t, text, mode)
+        x, cos, sin, cos_sin, temb, temb6, ctx, grid = self._embed(latent, t, text, mode)
         L = x.shape[0]
         P = dist.get_world_size(group) if group is not None else 1
         if P > 1:
@@ -391,9 +473,9 @@ class WanDiT:
                 raise ValueError(f"tokens ({L}) must divide by the world size ({P})")
             r = dist.get_rank(group)
             sl = slice(r * (L // P), (r + 1) * (L // P))
-            x, cos, sin = x[sl].contiguous(), cos[sl], sin[sl]
+            x, cos, sin, cos_sin = x[sl].contiguous(), cos[sl], sin[sl], cos_sin[sl].contiguous()
         for blk in self.blocks:
-            x = blk.forward(x, ctx, temb6, cos, sin, mode, group if P > 1 else None)
+            x = blk.forward(x, ctx, temb6, cos, sin, mode, group if P > 1 else None, cos_sin)
         y = self._head(x, temb, mode)
         if P > 1:
             parts = [torch.empty_like(y) for _ in range(P)]
@@ -407,10 +489,10 @@ class WanDiT:
         block ``(cosine of the outputs, cosine of the block's own contribution out - in)``.
         This is the per-block statement of parity; the free-running step comparison on top of
         it also measures how fast FP4 re-quantization amplifies last-bit differences."""
-        x, cos, sin, temb, temb6, ctx, grid = self._embed(latent, t, text, "nvfp4")
+        x, cos, sin, cos_sin, temb, temb6, ctx, grid = self._embed(latent, t, text, "nvfp4")
         out = []
         for blk in self.blocks:
-            y = blk.forward(x, ctx, temb6, cos, sin, "nvfp4")
+            y = blk.forward(x, ctx, temb6, cos, sin, "nvfp4", None, cos_sin)
             ref = blk.forward(x, ctx, temb6, cos, sin, "dequant")
             out.append((_cosine(y, ref), _cosine(y.float() - x.float(), ref.float() - x.float())))
             x = y

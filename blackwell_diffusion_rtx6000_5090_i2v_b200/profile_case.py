@@ -2,6 +2,8 @@
 
     python -m blackwell_diffusion_rtx6000_5090_i2v_b200.profile_case gemm --m 8192 --n 9216 --k 3072
     python -m blackwell_diffusion_rtx6000_5090_i2v_b200.profile_case quantize --m 27280 --k 3072
+    python -m blackwell_diffusion_rtx6000_5090_i2v_b200.profile_case norm --m 27280 --k 3072
+    python -m blackwell_diffusion_rtx6000_5090_i2v_b200.profile_case rope --m 27280 --k 3072
 
 Each case holds well under a few GB on the device, launches the kernel
 ``--iters`` times after ``--warmup`` launches, and prints the CUDA-event time.
@@ -32,7 +34,7 @@ def _time(fn, warmup, iters):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "quantize", "amax"])
+    ap.add_argument("kernel", choices=["gemm", "quantize", "amax", "norm", "rope"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=9216)
     ap.add_argument("--k", type=int, default=3072)
@@ -54,6 +56,29 @@ def main():
         N.check_status()
         print(f"gemm M={a.m} N={a.n} K={a.k}: {ms:.4f} ms, "
               f"{2.0 * a.m * a.n * a.k / ms / 1e9:.1f} TFLOP/s")
+    elif a.kernel == "rope":
+        # q/k RMSNorm + rotary embedding over a [m, 3k] QKV tensor (k = heads * 128)
+        from . import dit
+        heads = a.k // 128
+        cfg = dit.WanDiTConfig(dim=a.k, heads=heads, ffn=a.k, layers=1, in_channels=16, out_channels=16)
+        qkv = student_t_bf16((a.m, 3 * a.k), 11, device="cuda")
+        cos, sin = dit.rope_tables(cfg, (1, 1, a.m), "cuda")
+        cs = dit.pack_rope_table(cos, sin)
+        gq = torch.ones(a.k, device="cuda")
+        ms = _time(lambda: dit.qk_norm_rope(qkv, heads, 128, gq, gq, 1e-6, cs), a.warmup, a.iters)
+        N.check_status()
+        nbytes = 2 * (2.0 + 2.0) * a.m * a.k          # q and k, read + written
+        print(f"qk_norm_rope [{a.m}, 3x{a.k}]: {ms:.4f} ms, {nbytes / ms / 1e6:.1f} GB/s")
+    elif a.kernel == "norm":
+        # LayerNorm + adaLN modulation + quantize: both sweeps per iteration
+        g = torch.Generator(device="cuda").manual_seed(9)
+        scale = torch.randn(a.k, generator=g, device="cuda") * 0.1
+        shift = torch.randn(a.k, generator=g, device="cuda") * 0.1
+        ms = _time(lambda: FP4Tensor.from_norm_mod(x, scale=scale, shift=shift), a.warmup, a.iters)
+        N.check_status()
+        n = a.m * a.k
+        print(f"norm+mod+quantize [{a.m}, {a.k}]: {ms:.4f} ms, algorithmic {2.5625 * n / ms / 1e6:.1f} "
+              f"GB/s, moved {4.5625 * n / ms / 1e6:.1f} GB/s")
     else:
         q = FP4Tensor.from_bfloat16(x, linear_scales=False)
         if a.kernel == "quantize":

@@ -147,6 +147,26 @@ NVFP4_API int nvfp4_norm_mod_quantize_bf16(const void* x_bf16, int64_t rows, int
                                            uint8_t* scales_swizzled, float* global_scale_dev,
                                            int* status_dev, void* stream);
 
+/* q/k RMSNorm across heads + rotary embedding in one pass over the QKV linear's output: what
+ * the reference block does with separate torch ops between to_qkv and attention
+ * (fx/src/s4/models/wan22/wan_transformer.py:91-92,114-115 norm_q/norm_k; :61-75
+ * apply_rotary_emb).  q_in / k_in (/ v_in, nullable) are bf16 [rows, heads*head_dim] views
+ * with a common row stride in elements (e.g. the three column blocks of a [rows, 3*dim]
+ * tensor); gains are fp32 [heads*head_dim] or null for 1; cos_sin is fp32
+ * [rows, head_dim/2, 2] = (cos, sin) of each rotated pair.  Element (row, head, d) of an
+ * output lands at out + row*out_row_stride + head*out_head_stride + d (strides in elements),
+ * so one call can fill either three [rows, heads, head_dim] tensors or one packed
+ * [rows, heads, 3*head_dim] buffer; v is copied unchanged when given.  k_in/k_out may be null
+ * (q only), and cos_sin may be null (RMSNorm only, as for the cross-attention query).
+ * head_dim % 16 == 0, heads*head_dim <= 8192, strides % 8 == 0.  A row group that does not
+ * arrive in shared memory within about two seconds stores 0xA00 in *status_dev (nullable). */
+NVFP4_API int nvfp4_qk_norm_rope_bf16(const void* q_in, const void* k_in, const void* v_in,
+                                      int64_t in_row_stride, int64_t rows, int heads,
+                                      int head_dim, const float* gain_q, const float* gain_k,
+                                      float eps, const float* cos_sin, void* q_out, void* k_out,
+                                      void* v_out, int64_t out_row_stride,
+                                      int64_t out_head_stride, int* status_dev, void* stream);
+
 /* Has no counterpart in the reference.  One whole linear, y = act(x W^T + bias), for
  * callers that cannot allocate device memory (code inside a region where cudaMalloc is not
  * allowed, fixed-budget real-time loops, plug-ins handed only input and output pointers):

@@ -117,3 +117,47 @@ def test_flop_counts():
     per_block = m.linear_flops(27280) / cfg.layers
     assert abs(per_block / 1e12 - 7.92) < 0.03
     assert abs(m.attention_flops(27280) / 1e12 - 279.5) < 1.0
+
+
+@pytest.mark.parametrize("L,heads,packed", [(301, 4, False), (64, 24, True), (7, 40, False)])
+def test_fused_qk_norm_rope_matches_torch_ops(L, heads, packed):
+    """The fused q/k RMSNorm + rotary kernel against the separate torch ops of the comparison
+    model: same roundings, so equal except where the row's sum of squares (another summation
+    order) moves rstd by an ulp."""
+    from blackwell_diffusion_rtx6000_5090_i2v_b200 import dit, nvfp4
+    D = 128
+    cfg = dit.WanDiTConfig(dim=heads * D, heads=heads, ffn=1024, layers=1, in_channels=16, out_channels=16)
+    g = torch.Generator(device="cuda").manual_seed(L + heads)
+    qkv = (torch.randn(L, 3 * heads * D, generator=g, device="cuda") * 2).to(torch.bfloat16)
+    gq = 1 + 0.1 * torch.randn(heads * D, generator=g, device="cuda")
+    gk = 1 + 0.1 * torch.randn(heads * D, generator=g, device="cuda")
+    grid = (1, 1, L)
+    cos, sin = dit.rope_tables(cfg, grid, "cuda")
+    cs = dit.pack_rope_table(cos, sin)
+    q, k, v = qkv.chunk(3, dim=-1)
+    q_ref = dit.apply_rope(dit.rms_norm(q, gq, cfg.eps).view(L, heads, D), cos, sin)
+    k_ref = dit.apply_rope(dit.rms_norm(k, gk, cfg.eps).view(L, heads, D), cos, sin)
+    if packed:
+        out = dit.qk_norm_rope(qkv, heads, D, gq, gk, cfg.eps, cs, packed=True)
+        qf, kf, vf = out.split(D, dim=-1)
+    else:
+        qf, kf, vf = dit.qk_norm_rope(qkv, heads, D, gq, gk, cfg.eps, cs)
+    nvfp4.check_status()
+    assert torch.equal(vf, v.reshape(L, heads, D))
+    for got, ref in ((qf, q_ref), (kf, k_ref)):
+        diff = (got.float() - ref.float()).abs()
+        assert float((got != ref).float().mean()) < 5e-3
+        # where they differ it is by an ulp of the normalized value (about 1) entering the rotation
+        assert bool((diff <= 2.0 ** -7 * ref.float().abs() + 2.0 ** -6).all())
+
+
+def test_fused_rms_norm_only():
+    from blackwell_diffusion_rtx6000_5090_i2v_b200 import dit, nvfp4
+    g = torch.Generator(device="cuda").manual_seed(17)
+    x = (torch.randn(130, 5120, generator=g, device="cuda") * 3).to(torch.bfloat16)
+    gain = 1 + 0.1 * torch.randn(5120, generator=g, device="cuda")
+    got = dit.rms_norm_fused(x, 40, 128, gain, 1e-6)
+    nvfp4.check_status()
+    ref = dit.rms_norm(x, gain, 1e-6).view(130, 40, 128)
+    assert float((got != ref).float().mean()) < 5e-3
+    assert bool(((got.float() - ref.float()).abs() <= 2.0 ** -7 * ref.float().abs()).all())
