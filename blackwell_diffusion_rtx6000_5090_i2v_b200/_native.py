@@ -42,6 +42,8 @@ SIGNATURES = {
                                           _p, _p]),
     "nvfp4_qk_norm_rope_bf16": (_i, [_p, _p, _p, _i64, _i64, _i, _i, _p, _p, _f, _p, _p, _p, _p,
                                      _i64, _i64, _p, _p]),
+    "nvfp4_qk_norm_rope_exchange_bf16": (_i, [_p, _p, _p, _i64, _i64, _i, _i, _p, _p, _f, _p, _p, _i,
+                                              _i64, _p, _p]),
     "nvfp4_linear_bf16_static": (_i, [_p, _i64, _i64, _p, _p, _p, _i64, _p, _i, _p, _p, _p]),
     "nvfp4_linear_bf16_static_max_elements": (_i64, []),
 }

@@ -40,6 +40,11 @@ struct RopeArgs {
   int64_t out_row_bytes;
   int64_t out_head_bytes;
   int* status;
+  // exchange form: heads are dealt out to `world` ranks, each of which receives its heads of
+  // ALL tokens in a packed [tokens_total, heads_per_rank, 3 * head_dim] buffer
+  uint8_t* peer[8];            // that buffer on every rank (this rank's own included)
+  int heads_per_rank;          // 0: plain form
+  int64_t row_offset;          // this rank's first token in the global order
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -101,7 +106,7 @@ qk_norm_rope_kernel(const RopeArgs p) {
   const uint32_t slot_bytes = row_bytes * kR;
   const int64_t groups = (p.rows + kR - 1) / kR;
   const uint8_t* in = which == 0 ? p.in[0] : (which == 1 ? p.in[1] : p.in[2]);
-  uint8_t* out = which == 0 ? p.out[0] : (which == 1 ? p.out[1] : p.out[2]);
+  uint8_t* out = which == 0 ? p.out[0] : (which == 1 ? p.out[1] : p.out[2]);   // plain form
   const float* gain_ptr = which == 0 ? p.gain[0] : (which == 1 ? p.gain[1] : nullptr);
 
   auto issue = [&](int64_t g, int slot) {
@@ -136,7 +141,17 @@ qk_norm_rope_kernel(const RopeArgs p) {
   const int col = live ? u * 16 : 0;
   const int head = col / p.head_dim;
   const int d0 = col - head * p.head_dim;
-  const int64_t out_off = (int64_t)head * p.out_head_bytes + (int64_t)d0 * 2;
+  int64_t out_off = (int64_t)head * p.out_head_bytes + (int64_t)d0 * 2;
+  if (p.heads_per_rank > 0) {
+    // plain stores into the owner rank's buffer (its own memory or a peer's over NVLink)
+    const int dst = head / p.heads_per_rank;
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+      if (r == dst) out = p.peer[r];
+    out_off = p.row_offset * p.out_row_bytes +
+              (int64_t)(head - dst * p.heads_per_rank) * p.out_head_bytes +
+              (int64_t)(which * p.head_dim + d0) * 2;
+  }
   float2 gain[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) gain[e] = make_float2(1.0f, 1.0f);
@@ -269,6 +284,24 @@ qk_norm_rope_kernel(const RopeArgs p) {
   }
 }
 
+int launch_rope(RopeArgs& a, int tensors, cudaStream_t st) {
+  const int threads = (a.dim / 16 + 31) / 32 * 32;
+  const size_t smem = (size_t)kStages * kR * a.dim * 2;
+  if (cudaFuncSetAttribute(qk_norm_rope_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (int)smem) != cudaSuccess)
+    return NVFP4_ERR_LAUNCH_FAILED;
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, qk_norm_rope_kernel, threads, smem) !=
+          cudaSuccess || per_sm < 1)
+    return NVFP4_ERR_LAUNCH_FAILED;
+  const int64_t groups = (a.rows + kR - 1) / kR;
+  int64_t gx = ((int64_t)sm_count() * per_sm + tensors - 1) / tensors;
+  if (gx > groups) gx = groups;
+  if (gx < 1) gx = 1;
+  qk_norm_rope_kernel<<<dim3((unsigned)gx, (unsigned)tensors), threads, smem, st>>>(a);
+  return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_ERR_LAUNCH_FAILED;
+}
+
 }  // namespace
 }  // namespace nvfp4
 
@@ -314,21 +347,47 @@ extern "C" NVFP4_API int nvfp4_qk_norm_rope_bf16(const void* q_in, const void* k
   a.out_row_bytes = out_row_stride * 2;
   a.out_head_bytes = out_head_stride * 2;
   a.status = status_dev;
-  const int threads = (int)((dim / 16 + 31) / 32 * 32);
-  const size_t smem = (size_t)kStages * kR * dim * 2;
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (cudaFuncSetAttribute(qk_norm_rope_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           (int)smem) != cudaSuccess)
-    return NVFP4_ERR_LAUNCH_FAILED;
-  int per_sm = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, qk_norm_rope_kernel, threads, smem) !=
-          cudaSuccess || per_sm < 1)
-    return NVFP4_ERR_LAUNCH_FAILED;
-  const int tensors = v_in ? 3 : (k_in ? 2 : 1);
-  const int64_t groups = (rows + kR - 1) / kR;
-  int64_t gx = ((int64_t)sm_count() * per_sm + tensors - 1) / tensors;
-  if (gx > groups) gx = groups;
-  if (gx < 1) gx = 1;
-  qk_norm_rope_kernel<<<dim3((unsigned)gx, (unsigned)tensors), threads, smem, st>>>(a);
-  return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_ERR_LAUNCH_FAILED;
+  return launch_rope(a, v_in ? 3 : (k_in ? 2 : 1), reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" NVFP4_API int nvfp4_qk_norm_rope_exchange_bf16(
+    const void* q_in, const void* k_in, const void* v_in, int64_t in_row_stride, int64_t rows,
+    int heads, int head_dim, const float* gain_q, const float* gain_k, float eps,
+    const float* cos_sin, void* const* rank_buffers, int world, int64_t row_offset,
+    int* status_dev, void* stream) {
+  const int64_t dim = (int64_t)heads * head_dim;
+  if (rows < 0 || heads <= 0 || head_dim <= 0 || head_dim % 16 != 0 || dim > 16 * kMaxThreads ||
+      in_row_stride < dim || in_row_stride % 8 != 0 || world < 1 || world > 8 ||
+      heads % world != 0 || row_offset < 0 || !rank_buffers)
+    return NVFP4_ERR_BAD_ARG;
+  if (rows > 0 && (!q_in || !k_in || !v_in)) return NVFP4_ERR_BAD_ARG;
+  if (!aligned16(q_in) || !aligned16(k_in) || !aligned16(v_in) || !aligned16(gain_q) ||
+      !aligned16(gain_k) || !aligned16(cos_sin))
+    return NVFP4_ERR_BAD_ALIGN;
+  for (int r = 0; r < world; ++r) {
+    if (!rank_buffers[r]) return NVFP4_ERR_BAD_ARG;
+    if (!aligned16(rank_buffers[r])) return NVFP4_ERR_BAD_ALIGN;
+  }
+  int rc = check_device_sm100();
+  if (rc != NVFP4_OK) return rc;
+  if (rows == 0) return NVFP4_OK;
+  RopeArgs a{};
+  a.in[0] = static_cast<const uint8_t*>(q_in);
+  a.in[1] = static_cast<const uint8_t*>(k_in);
+  a.in[2] = static_cast<const uint8_t*>(v_in);
+  a.in_row_bytes = in_row_stride * 2;
+  a.rows = rows;
+  a.dim = (int)dim;
+  a.head_dim = head_dim;
+  a.gain[0] = gain_q;
+  a.gain[1] = gain_k;
+  a.eps = eps;
+  a.cos_sin = reinterpret_cast<const float2*>(cos_sin);
+  a.heads_per_rank = heads / world;
+  a.out_head_bytes = (int64_t)3 * head_dim * 2;
+  a.out_row_bytes = (int64_t)a.heads_per_rank * a.out_head_bytes;
+  a.row_offset = row_offset;
+  for (int r = 0; r < world; ++r) a.peer[r] = static_cast<uint8_t*>(rank_buffers[r]);
+  a.status = status_dev;
+  return launch_rope(a, 3, reinterpret_cast<cudaStream_t>(stream));
 }

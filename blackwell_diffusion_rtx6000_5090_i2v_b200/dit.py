@@ -284,10 +284,28 @@ class WanBlock:
         self._amax = torch.empty(1, dtype=torch.float32, device=device)
 
     # ---------------------------------------------------------------- parts --
-    def _self_attention_fused(self, qkv, cos_sin, group):
+    def _self_attention_fused(self, qkv, cos_sin, group, px=None):
         """nvfp4 path: one kernel between the QKV linear and attention (or the exchange)."""
         cfg = self.cfg
         L = qkv.shape[0]
+        if px is not None:
+            # exchange by stores into peer memory, fused into the norm + RoPE kernel
+            dim = cfg.dim
+            base = qkv.data_ptr()
+            N.check(N.lib.nvfp4_qk_norm_rope_exchange_bf16(
+                base, base + 2 * dim, base + 4 * dim, 3 * dim, L, cfg.heads, cfg.head_dim,
+                N.ptr(self.g_q), N.ptr(self.g_k), float(cfg.eps), N.ptr(cos_sin),
+                px.qkv_ptrs[px.turn], px.P, px.rank * px.Lp, N.ptr(N.status_word(qkv.device)),
+                N.stream_ptr()), "qk_norm_rope_exchange")
+            _mark("qk_norm_rope")
+            px.barrier()
+            q, k, v = px.qkv[px.turn].split(cfg.head_dim, dim=-1)
+            _mark("exchange")
+            o = attention(q, k, v)
+            _mark("self_attention")
+            o = px.scatter_attention_output(o)
+            _mark("exchange")
+            return o.reshape(L, cfg.dim)
         if group is None:
             q, k, v = qk_norm_rope(qkv, cfg.heads, cfg.head_dim, self.g_q, self.g_k, cfg.eps, cos_sin)
             _mark("qk_norm_rope")
@@ -334,7 +352,8 @@ class WanBlock:
 
     # -------------------------------------------------------------- forward --
     def forward(self, x: torch.Tensor, ctx: torch.Tensor, temb6: torch.Tensor, cos, sin,
-                mode: str = "nvfp4", group=None, cos_sin: Optional[torch.Tensor] = None) -> torch.Tensor:
+                mode: str = "nvfp4", group=None, cos_sin: Optional[torch.Tensor] = None,
+                px: Optional[ulysses.PeerExchange] = None) -> torch.Tensor:
         cfg = self.cfg
         mod = self.scale_shift_table + temb6.float()
         shift_msa, scale_msa, gate_msa, c_shift, c_scale, c_gate = (m.contiguous() for m in mod)
@@ -347,7 +366,7 @@ class WanBlock:
             _mark("norm_quantize")
             qkv = self.qkv.nvfp4(a)
             _mark("gemm")
-            o = self._self_attention_fused(qkv, cos_sin, group)
+            o = self._self_attention_fused(qkv, cos_sin, group, px)
             oq = FP4Tensor.from_bfloat16(o.contiguous(), linear_scales=False)
             _mark("quantize")
             x = self.attn_out.nvfp4(oq, gate=gate_msa, C=x, beta=1.0)
@@ -411,6 +430,7 @@ class WanDiT:
         self.blocks: List[WanBlock] = [WanBlock(cfg, gen, self.device)
                                        for _ in range(layers if layers is not None else cfg.layers)]
         self._rope: Dict[Tuple[int, int, int], Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = {}
+        self._px: Dict[Tuple[int, int], ulysses.PeerExchange] = {}
         self.out_table = torch.randn(2, d, generator=gen, device=self.device) / d ** 0.5
         self.proj_out = PackedLinear(cfg.out_channels * pt * ph * pw, d, gen, self.device)
 
@@ -461,10 +481,12 @@ class WanDiT:
         return y.reshape(cfg.out_channels, f * pt, h * ph, w * pw)
 
     def forward(self, latent: torch.Tensor, t: float, text: torch.Tensor, mode: str = "nvfp4",
-                group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+                group: Optional[dist.ProcessGroup] = None, exchange: str = "nccl") -> torch.Tensor:
         """latent ``[C, F, H, W]`` bf16, text ``[512, 4096]`` bf16 -> ``[C_out, F, H, W]``.
         With ``group`` each rank processes its contiguous shard of the token sequence and
-        returns the full output (gathered) on every rank."""
+        returns the full output (gathered) on every rank.  ``exchange``: ``"nccl"`` (two
+        all-to-alls per block) or ``"peer"`` (stores into peer memory fused into the q/k norm +
+        RoPE kernel; NVFP4 mode, ranks of one node)."""
         x, cos, sin, cos_sin, temb, temb6, ctx, grid = self._embed(latent, t, text, mode)
         L = x.shape[0]
         P = dist.get_world_size(group) if group is not None else 1
@@ -474,8 +496,14 @@ class WanDiT:
             r = dist.get_rank(group)
             sl = slice(r * (L // P), (r + 1) * (L // P))
             x, cos, sin, cos_sin = x[sl].contiguous(), cos[sl], sin[sl], cos_sin[sl].contiguous()
+        px = None
+        if P > 1 and exchange == "peer" and mode == "nvfp4":
+            key = (L, id(group))
+            if key not in self._px:
+                self._px[key] = ulysses.PeerExchange(L, cfg.heads, cfg.head_dim, group, self.device)
+            px = self._px[key]
         for blk in self.blocks:
-            x = blk.forward(x, ctx, temb6, cos, sin, mode, group if P > 1 else None, cos_sin)
+            x = blk.forward(x, ctx, temb6, cos, sin, mode, group if P > 1 else None, cos_sin, px)
         y = self._head(x, temb, mode)
         if P > 1:
             parts = [torch.empty_like(y) for _ in range(P)]

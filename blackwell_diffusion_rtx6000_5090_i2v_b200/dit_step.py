@@ -38,6 +38,8 @@ def main(argv=None) -> int:
     ap.add_argument("--warmup", type=int, default=1)
     ap.add_argument("--check", action="store_true", help="cosine against the dequant model")
     ap.add_argument("--sdpa", choices=["default", "flash", "cudnn"], default="default")
+    ap.add_argument("--exchange", choices=["nccl", "peer"], default="nccl",
+                    help="head/sequence exchange: all-to-alls, or stores into peer memory")
     args = ap.parse_args(argv)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -66,12 +68,12 @@ def main(argv=None) -> int:
         from torch.nn.attention import SDPBackend
         backends = [SDPBackend.FLASH_ATTENTION if args.sdpa == "flash" else SDPBackend.CUDNN_ATTENTION]
 
-    def step(mode="nvfp4", grp=group):
+    def step(mode="nvfp4", grp=group, exchange=args.exchange):
         if backends is not None:
             from torch.nn.attention import sdpa_kernel
             with sdpa_kernel(backends):
-                return model.forward(latent, 500.0, text, mode=mode, group=grp)
-        return model.forward(latent, 500.0, text, mode=mode, group=grp)
+                return model.forward(latent, 500.0, text, mode=mode, group=grp, exchange=exchange)
+        return model.forward(latent, 500.0, text, mode=mode, group=grp, exchange=exchange)
 
     def fence():
         if world > 1:
@@ -114,6 +116,10 @@ def main(argv=None) -> int:
                 per_block = model.compare_blocks(latent, 500.0, text)
                 checks["per_block_same_input_cosine_min"] = min(c for c, _ in per_block)
                 checks["per_block_same_input_delta_cosine_min"] = min(d for _, d in per_block)
+            if world > 1 and args.exchange == "peer":
+                other = step(exchange="nccl")
+                checks["peer_exchange_equals_nccl_exchange"] = bool(torch.equal(y, other))
+                del other
             if world > 1:
                 fence()
                 if rank == 0:
@@ -132,6 +138,7 @@ def main(argv=None) -> int:
             "config": {"workload": f"wan2.2 {args.config} shape, {len(model.blocks)} blocks, "
                                    f"{tokens} tokens, text 512x{cfg.text_dim}",
                        "tokens_per_rank": tokens // world, "sdpa": args.sdpa,
+                       "exchange": args.exchange if world > 1 else None,
                        "parallelism": f"ulysses{world}" if world > 1 else "single"},
             "all_ms": [round(t, 3) for t in times],
             "components_ms_rank0": {k: round(v, 3) for k, v in sorted(parts.items())},

@@ -192,6 +192,40 @@ class FP4Tensor:
                     "[tensor] norm+quantize")
         return (self, normed) if return_normed else self
 
+    @staticmethod
+    def from_packed(data: torch.Tensor, scales: torch.Tensor, amax: torch.Tensor,
+                    global_scale: torch.Tensor, shape: Sequence[int]) -> "FP4Tensor":
+        """Re-create a packed tensor from stored parts (additive: the reference never stores
+        one): ``data`` uint8 ``[numel/2]``, ``scales`` uint8 linear ``[numel/16]``, ``amax`` and
+        ``global_scale`` one-element fp32, all on one CUDA device; ``shape`` with a last
+        dimension that is a multiple of 16.  The tensor-core scale layout is rebuilt on first use."""
+        shape = [int(v) for v in shape]
+        if len(shape) < 1 or shape[-1] % FP4_BLOCK_SIZE != 0:
+            raise RuntimeError("[s4] [nvfp4] [tensor] stored shape needs a last dimension % 16 == 0")
+        numel = 1
+        for v in shape:
+            numel *= v
+        dev = data.device
+        if not data.is_cuda or data.dtype != torch.uint8 or scales.dtype != torch.uint8 or \
+                data.numel() != numel // 2 or scales.numel() != numel // FP4_BLOCK_SIZE:
+            raise RuntimeError("[s4] [nvfp4] [tensor] stored buffers do not match the shape")
+        for t in (scales, amax, global_scale):
+            if t.device != dev:
+                raise RuntimeError("[s4] [nvfp4] [tensor] stored buffers must share one device")
+        if amax.dtype != torch.float32 or global_scale.dtype != torch.float32 or \
+                amax.numel() != 1 or global_scale.numel() != 1:
+            raise RuntimeError("[s4] [nvfp4] [tensor] amax / global_scale must be one-element float32")
+        self = object.__new__(FP4Tensor)
+        self._shape, self._mode, self._device, self._numel = shape, QuantizationMode.block_1d, dev, numel
+        self._cols = shape[-1]
+        self._rows = numel // self._cols
+        self._data = data.contiguous().reshape(-1)
+        self._scales = scales.contiguous().reshape(-1)
+        self._scales_swz = None
+        self._amax = amax.contiguous().reshape(1)
+        self._gscale = global_scale.contiguous().reshape(1)
+        return self
+
     # ------------------------------------------------------------ access --
     def to_bfloat16(self) -> torch.Tensor:
         """Dequantize (fx/src/s4/nvfp4/tensor.h:53-72)."""

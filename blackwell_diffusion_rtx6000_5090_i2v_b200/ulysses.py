@@ -64,3 +64,61 @@ def exchange_bytes_per_rank(tokens: int, heads: int, head_dim: int, world: int,
     (P-1)/P leaves the GPU."""
     per_tensor = tokens // world * heads * head_dim * elem_bytes
     return tensors * per_tensor * (world - 1) // world
+
+
+class PeerExchange:
+    """The two exchanges of a block done by stores into peer memory instead of all-to-alls.
+
+    Every rank holds, in symmetric memory mapped by all ranks of the node, a packed
+    ``[L, H/P, 3D]`` buffer (its heads of q | k | v for ALL tokens) and an ``[L/P, H, D]`` buffer
+    (all heads of the attention output for ITS tokens).  The q/k norm + RoPE kernel of each rank
+    stores its tokens' pieces straight into the owning ranks' packed buffers over NVLink
+    (``nvfp4_qk_norm_rope_exchange_bf16``), and after attention each rank copies its heads'
+    output rows into the owning ranks' output buffers.  What remains of the collective is one
+    tiny all-reduce after each set of stores, which orders the consumers on every rank after
+    the producers on all ranks.  Two sets of buffers alternate from block to block: a rank can
+    be at most one barrier ahead of a peer, so it never overwrites a buffer a peer still reads.
+
+    Plain loads and stores only -- no multicast mapping is created or used.
+    """
+
+    def __init__(self, tokens_total: int, heads: int, head_dim: int, group: dist.ProcessGroup,
+                 device: torch.device):
+        import ctypes
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm
+        P, r = dist.get_world_size(group), dist.get_rank(group)
+        if heads % P or tokens_total % P:
+            raise ValueError("heads and tokens must divide by the world size")
+        self.group, self.P, self.rank = group, P, r
+        self.L, self.Lp, self.H, self.Hp, self.D = tokens_total, tokens_total // P, heads, heads // P, head_dim
+        self.qkv, self.o, self.qkv_ptrs, self.o_peer = [], [], [], []
+        for _ in range(2):
+            t = symm.empty((self.L, self.Hp, 3 * head_dim), dtype=torch.bfloat16, device=device)
+            h = symm.rendezvous(t, group)
+            self.qkv.append(t)
+            self.qkv_ptrs.append((ctypes.c_void_p * P)(*[int(p) for p in h.buffer_ptrs]))
+            t = symm.empty((self.Lp, heads, head_dim), dtype=torch.bfloat16, device=device)
+            h = symm.rendezvous(t, group)
+            self.o.append(t)
+            self.o_peer.append([h.get_buffer(s, (self.Lp, heads, head_dim), torch.bfloat16)
+                                for s in range(P)])
+        self._flag = torch.zeros(1, dtype=torch.float32, device=device)
+        self.turn = 0
+
+    def barrier(self) -> None:
+        """Stream-ordered: every rank's work enqueued before it is complete on every rank
+        before anything enqueued after it starts."""
+        dist.all_reduce(self._flag, group=self.group)
+
+    def scatter_attention_output(self, o: torch.Tensor) -> torch.Tensor:
+        """``o`` is ``[L, H/P, D]`` (my heads, all tokens).  Store each rank's token rows into its
+        output buffer and return mine, ``[L/P, H, D]``, once every rank has done the same."""
+        i, r, Lp, Hp = self.turn, self.rank, self.Lp, self.Hp
+        for s in range(self.P):
+            self.o_peer[i][s][:, r * Hp:(r + 1) * Hp, :].copy_(o[s * Lp:(s + 1) * Lp])
+        self.barrier()
+        out = self.o[i]
+        self.turn ^= 1
+        return out

@@ -167,6 +167,22 @@ NVFP4_API int nvfp4_qk_norm_rope_bf16(const void* q_in, const void* k_in, const 
                                       void* v_out, int64_t out_row_stride,
                                       int64_t out_head_stride, int* status_dev, void* stream);
 
+/* The same kernel fused with the head/sequence exchange of sequence-parallel attention (no
+ * reference counterpart: the reference has no distributed code).  `heads` are dealt out to
+ * `world` ranks in order; rank_buffers[r] (a HOST array of `world` device pointers) is rank r's
+ * bf16 [tokens_total, heads/world, 3*head_dim] buffer as mapped in THIS process (its own buffer
+ * for r = this rank, peer-mapped memory otherwise).  Each thread stores its q | k | v pieces of
+ * this rank's `rows` tokens, global token index row_offset + row, straight into the buffer of
+ * the rank that owns the head: plain stores over NVLink, no staging copy, no collective.  The
+ * caller orders the consumers after all ranks' kernels (a barrier on the same streams). */
+NVFP4_API int nvfp4_qk_norm_rope_exchange_bf16(const void* q_in, const void* k_in, const void* v_in,
+                                               int64_t in_row_stride, int64_t rows, int heads,
+                                               int head_dim, const float* gain_q,
+                                               const float* gain_k, float eps,
+                                               const float* cos_sin, void* const* rank_buffers,
+                                               int world, int64_t row_offset, int* status_dev,
+                                               void* stream);
+
 /* Has no counterpart in the reference.  One whole linear, y = act(x W^T + bias), for
  * callers that cannot allocate device memory (code inside a region where cudaMalloc is not
  * allowed, fixed-budget real-time loops, plug-ins handed only input and output pointers):
