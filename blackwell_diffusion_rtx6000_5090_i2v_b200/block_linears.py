@@ -136,3 +136,19 @@ class WanBlockLinears:
             else:
                 self.gemm(s, st, amax_next)
         return self.out
+
+    def capture(self, inputs: Dict[str, torch.Tensor]) -> "torch.cuda.CUDAGraph":
+        """Record one :meth:`step` over ``inputs`` into a CUDA graph (the static-shape capture of
+        fx/src/s4/models/wan_22/wan_attention_static.py:566-630, for this path's launches).  The
+        step allocates nothing and never synchronises with the host, so the graph holds exactly
+        its kernels and memsets; ``graph.replay()`` re-runs them on whatever the input tensors
+        then contain, results in ``self.out``."""
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            self.step(inputs)                       # warm-up outside the capture
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.step(inputs)
+        return graph

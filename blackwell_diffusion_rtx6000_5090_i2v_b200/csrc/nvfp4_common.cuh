@@ -46,15 +46,15 @@ __device__ __forceinline__ float global_encode_scale(float amax) {
   return s;
 }
 
-// x / 6 for finite x >= 0, bit-identical to the IEEE quotient: one multiply by fl(1/6) and one
-// residual correction (two FMAs).  The residual of a tiny quotient is itself inexact, so very
-// small x takes the division.  Checked against x / 6.0f for every bf16 x >= 1e-30 and two
-// million fp32 values.
+// x / 6, bit-identical to the IEEE quotient: one multiply by fl(1/6) and one residual
+// correction (two FMAs).  The residual of a tiny quotient is itself inexact and that of an
+// infinite one is NaN, so very small, very large and non-finite x take the division.  Checked
+// against x / 6.0f for every bf16 x in the fast range and two million fp32 values.
 __device__ __forceinline__ float div_by_6(float x) {
   const float c = 0x1.555556p-3f;
   const float q0 = __fmul_rn(x, c);
   const float q = __fmaf_rn(__fmaf_rn(-6.0f, q0, x), c, q0);
-  return x < 1e-30f ? __fdiv_rn(x, 6.0f) : q;
+  return (x >= 1e-30f && x <= 1e37f) ? q : __fdiv_rn(x, 6.0f);
 }
 
 // E4M3 block scale: rn_satfinite( min( (amax_b / 6) * S_enc, FLT_MAX ) ).

@@ -74,7 +74,9 @@ quantize_bf16_kernel(const uint4* __restrict__ x, uint32_t n_blocks, uint32_t kb
   const float s_dec = __fdiv_rn(1.0f, s_enc);
   if (global_scale_out && blockIdx.x == 0 && threadIdx.x == 0) *global_scale_out = s_dec;
 
-  const uint32_t base = blockIdx.x * (kThreads * kBlocksPerThread) + threadIdx.x;
+  // CTAs start at the END of the tensor: the amax pass that ran just before walked it
+  // forwards, so its tail is what is still in L2 (126 MB) when this kernel begins
+  const uint32_t base = (gridDim.x - 1u - blockIdx.x) * (kThreads * kBlocksPerThread) + threadIdx.x;
   uint4 v[kBlocksPerThread][2];
 #pragma unroll
   for (int j = 0; j < kBlocksPerThread; ++j) {
@@ -97,22 +99,23 @@ quantize_bf16_kernel(const uint4* __restrict__ x, uint32_t n_blocks, uint32_t kb
     const uint32_t b = base + j * kThreads;
     const uint32_t w[8] = {v[j][0].x, v[j][0].y, v[j][0].z, v[j][0].w,
                            v[j][1].x, v[j][1].y, v[j][1].z, v[j][1].w};
-    float f[16];
+    // block amax on the packed pairs (exact: the values are bf16), then widen once
+    uint32_t a2 = 0u;
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      f[2 * k] = bf16lo_to_f32(w[k]);
-      f[2 * k + 1] = bf16hi_to_f32(w[k]);
-    }
-    float amax_b = 0.0f;
+    for (int k = 0; k < 8; ++k) a2 = bf16x2_max_abs(a2, w[k]);
+    const float amax_b = fmaxf(bf16lo_to_f32(a2), bf16hi_to_f32(a2));
+    // (amax_b / 6) * S_enc -> E4M3; 1 / (float(sf) * S_dec): both quotients IEEE-rounded
+    float d = __fmul_rn(div_by_6(amax_b), s_enc);
+    d = fminf(d, FLT_MAX);
+    const uint8_t sf = (uint8_t)__nv_cvt_float_to_fp8(d, __NV_SATFINITE, __NV_E4M3);
+    const float enc = fminf(__frcp_rn(__fmul_rn(e4m3_to_f32(sf), s_dec)), FLT_MAX);
+    const float2 enc2 = make_float2(enc, enc);
+    float2 q[8];
 #pragma unroll
-    for (int k = 0; k < 16; ++k) amax_b = fmaxf(amax_b, fabsf(f[k]));
-    const uint8_t sf = block_scale_e4m3(amax_b, s_enc);
-    const float enc = block_encode_scale(sf, s_dec);
-#pragma unroll
-    for (int k = 0; k < 16; ++k) f[k] = __fmul_rn(f[k], enc);
+    for (int k = 0; k < 8; ++k) q[k] = f2_mul(bf16x2_to_f2(w[k]), enc2);
     uint2 out;
-    out.x = f32x8_to_e2m1x8(f[0], f[1], f[2], f[3], f[4], f[5], f[6], f[7]);
-    out.y = f32x8_to_e2m1x8(f[8], f[9], f[10], f[11], f[12], f[13], f[14], f[15]);
+    out.x = f32x8_to_e2m1x8(q[0].x, q[0].y, q[1].x, q[1].y, q[2].x, q[2].y, q[3].x, q[3].y);
+    out.y = f32x8_to_e2m1x8(q[4].x, q[4].y, q[5].x, q[5].y, q[6].x, q[6].y, q[7].x, q[7].y);
     if (b < n_blocks) {
       __stcs(packed + b, out);
       if (sf_lin) sf_lin[b] = sf;

@@ -500,7 +500,7 @@ class WanDiT:
         if P > 1 and exchange == "peer" and mode == "nvfp4":
             key = (L, id(group))
             if key not in self._px:
-                self._px[key] = ulysses.PeerExchange(L, cfg.heads, cfg.head_dim, group, self.device)
+                self._px[key] = ulysses.PeerExchange(L, self.cfg.heads, self.cfg.head_dim, group, self.device)
             px = self._px[key]
         for blk in self.blocks:
             x = blk.forward(x, ctx, temb6, cos, sin, mode, group if P > 1 else None, cos_sin, px)
