@@ -323,3 +323,26 @@ int nvfp4_oracle_linear(const uint16_t* x, const uint16_t* w, const uint16_t* bi
   free(xp); free(xs); free(wp); free(ws); free(xq); free(wq);
   return rc;
 }
+
+/* Check of a device-side shortcut, not part of the restated algorithm: the kernels form x / 6
+ * as q0 = x * fl(1/6), q = fma(fma(-6, q0, x), fl(1/6), q0) inside [1e-30, 1e37] and by IEEE
+ * division outside.  Returns the number of inputs among the n given for which that differs
+ * from x / 6.0f (the tests feed every bf16 value and a few million fp32 values: expect 0). */
+int64_t nvfp4_oracle_div6_mismatches(const float* x, int64_t n) {
+  const float c = 1.0f / 6.0f;
+  int64_t bad = 0;
+  for (int64_t i = 0; i < n; ++i) {
+    volatile float ref = x[i] / 6.0f;
+    float q;
+    if (x[i] >= 1e-30f && x[i] <= 1e37f) {
+      const float q0 = x[i] * c;
+      q = fmaf(fmaf(-6.0f, q0, x[i]), c, q0);
+    } else {
+      q = x[i] / 6.0f;
+    }
+    const float r = ref;
+    if (memcmp(&q, &r, sizeof q) != 0 && !(q != q && r != r)) ++bad;
+  }
+  return bad;
+}
+

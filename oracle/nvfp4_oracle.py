@@ -46,6 +46,8 @@ def lib():
         L.nvfp4_oracle_f32_to_e2m1.argtypes = [C.c_float]
         L.nvfp4_oracle_e2m1_to_f32.restype = C.c_float
         L.nvfp4_oracle_e2m1_to_f32.argtypes = [C.c_uint8]
+        L.nvfp4_oracle_div6_mismatches.restype = C.c_int64
+        L.nvfp4_oracle_div6_mismatches.argtypes = [p, i64]
         L.nvfp4_oracle_amax_bf16.restype = C.c_float
         L.nvfp4_oracle_amax_bf16.argtypes = [p, i64]
         L.nvfp4_oracle_global_encode_scale.restype = C.c_float

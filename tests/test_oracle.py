@@ -180,3 +180,16 @@ def test_epilogue_terms(oracle):
     z = 0.5 * z * (1 + np.tanh(0.7978845608028654 * (z + 0.044715 * z ** 3)))
     z = z * gate + oracle.bf16_bits_to_f32(res)
     assert np.allclose(y, z, rtol=1e-4, atol=1e-4)
+
+
+def test_fast_division_by_six_is_exact(oracle):
+    """The kernels' three-operation x / 6 equals IEEE division on every bf16 value (the only
+    inputs it ever sees: block maxima of bf16 tensors) and on a few million fp32 values."""
+    import numpy as np
+    lib = oracle.lib()
+    bf16 = (np.arange(1 << 16, dtype=np.uint32) << 16).view(np.float32)
+    rng = np.random.default_rng(6)
+    fp32 = rng.integers(0, 1 << 32, size=4_000_000, dtype=np.uint64).astype(np.uint32).view(np.float32)
+    for arr in (bf16, fp32):
+        a = np.ascontiguousarray(arr)
+        assert lib.nvfp4_oracle_div6_mismatches(a.ctypes.data, a.size) == 0
