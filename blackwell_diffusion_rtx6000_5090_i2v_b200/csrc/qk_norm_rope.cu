@@ -171,18 +171,7 @@ qk_norm_rope_kernel(const RopeArgs p) {
   int parity = 0;
   for (int64_t g = blockIdx.x; g < groups; g += gridDim.x, parity ^= 1) {
     const int64_t base = g * kR;
-    // this group's rotation table entries: asked for before the wait, used after the reduction
-    float4 cs[kR][4];
     const bool rotate = which < 2 && p.cos_sin != nullptr;
-    if (rotate) {
-#pragma unroll
-      for (int r = 0; r < kR; ++r) {
-        const int64_t row = base + r < p.rows ? base + r : base;
-        const float4* t = reinterpret_cast<const float4*>(p.cos_sin + row * half_hd + (d0 >> 1));
-#pragma unroll
-        for (int q = 0; q < 4; ++q) cs[r][q] = __ldg(t + q);
-      }
-    }
     wait_group(smem_u32(&full[slot]), phase, &abort_flag, p.status);
     const uint8_t* slot_ptr = ring + (size_t)slot * slot_bytes;
     uint32_t xp[kR][8];
@@ -244,6 +233,15 @@ qk_norm_rope_kernel(const RopeArgs p) {
     for (int r = 0; r < kR; ++r) {
       if (!(live && row_ok[r])) continue;
       uint32_t o[8];
+      // this token's rotation table entries (L1 / L2 hits: every head of the token reads the
+      // same 512 bytes); loaded here rather than ahead of the wait to keep registers, and with
+      // them the number of resident CTAs, in check
+      float4 cs[4];
+      if (rotate) {
+        const float4* t = reinterpret_cast<const float4*>(p.cos_sin + (base + r) * half_hd + (d0 >> 1));
+#pragma unroll
+        for (int q = 0; q < 4; ++q) cs[q] = __ldg(t + q);
+      }
       if (which < 2) {
         const float2 r2 = make_float2(rstd[r], rstd[r]);
         const float2 sign = make_float2(-1.0f, 1.0f);
@@ -256,7 +254,7 @@ qk_norm_rope_kernel(const RopeArgs p) {
             continue;
           }
           const float2 n = bf16x2_to_f2(nb);
-          const float4 t4 = cs[r][e >> 1];
+          const float4 t4 = cs[e >> 1];
           const float c = (e & 1) ? t4.z : t4.x, s = (e & 1) ? t4.w : t4.y;
           const float2 nc = f2_mul(n, make_float2(c, c));                      // (x1 c, x2 c)
           const float2 ns = f2_mul(make_float2(n.y, n.x), make_float2(s, s));  // (x2 s, x1 s)
