@@ -242,18 +242,32 @@ def run_ours(args, rank: int, local_rank: int, world: int):
     quant_gbs = 2.5625 * qa.m * qa.k / (q0.elapsed_time(q1) / reps * 1e-3) / 1e9
 
     # ---- fused LayerNorm + adaLN modulation + quantize (both sweeps), the block's norm1 shape ----
-    from blackwell_diffusion_rtx6000_5090_i2v_b200.nvfp4 import FP4Tensor
     xin = runner.out["attn_out"]                      # [M, dim] bf16
-    dim = xin.shape[1]
+    rows_n, dim = xin.shape
     gsc = torch.Generator(device="cuda").manual_seed(77)
     ada_scale = torch.randn(dim, generator=gsc, device="cuda") * 0.1
     ada_shift = torch.randn(dim, generator=gsc, device="cuda") * 0.1
+    qn = runner.act["qkv"]                            # packed buffers of a [M, dim] activation
+    stats = torch.empty(2 * rows_n, dtype=torch.float32, device="cuda")
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def fused_norm_quantize():
+        N.check(N.lib.nvfp4_norm_mod_amax_bf16(xin.data_ptr(), rows_n, dim, None, None,
+                                               ada_scale.data_ptr(), ada_shift.data_ptr(), 0, 1e-6,
+                                               stats.data_ptr(), qn.amax.data_ptr(), None,
+                                               runner.status.data_ptr(), st), "norm amax")
+        N.check(N.lib.nvfp4_norm_mod_quantize_bf16(xin.data_ptr(), rows_n, dim, None, None,
+                                                   ada_scale.data_ptr(), ada_shift.data_ptr(),
+                                                   stats.data_ptr(), qn.amax.data_ptr(),
+                                                   qn.data.data_ptr(), None, qn.sf.data_ptr(),
+                                                   qn.gscale.data_ptr(), runner.status.data_ptr(), st),
+                "norm quantize")
+
     fused_ms = []
     for i in range(3 + reps):
-        flush.zero_()
+        flush.zero_()                                 # L2 flush; also keeps the GPU ahead of the host
         q0.record()
-        FP4Tensor.from_norm_mod(xin, scale=ada_scale, shift=ada_shift)
+        fused_norm_quantize()
         q1.record()
         torch.cuda.synchronize()
         if i >= 3:
@@ -366,10 +380,10 @@ def run_ours(args, rank: int, local_rank: int, world: int):
                 "flops_per_launch_avg": runner.flops_per_step / len(specs),
                 "per_linear_tflops": per_linear,
                 "library_reference": lib_ref,
-                "traffic": 3.6e8,
+                "traffic": 3.46e8,
                 "traffic_source": "ncu dram read+write of the M=8192,N=9216,K=3072 capture "
-                                  "(127 MB) scaled by algorithmic bytes to the average launch "
-                                  "of this workload; bytes per launch",
+                                  "(122 MB for 181 MB algorithmic) scaled by algorithmic bytes to "
+                                  "the average launch of this workload (513 MB); bytes per launch",
             },
             "quantizer": {"kernel": "quantize_bf16_kernel", "bound": "hbm", "achieved": quant_gbs,
                           "peak": peaks["hbm_gbs"], "unit": "GB/s",
