@@ -75,3 +75,57 @@ class NVFP4Linear(nn.Module):
                                  device=input.device, dtype=torch.float32)
         return NVFP4LinearFunction.apply(input, self.weight, self.bias, scale_input,
                                          self.scale_weight)
+
+    @classmethod
+    def from_linear(cls, linear: nn.Linear, block_size: int = 32) -> "NVFP4Linear":
+        """An NVFP4Linear holding ``linear``'s weight and bias (cast to bf16), on its device."""
+        out = cls(linear.in_features, linear.out_features, linear.bias is not None, block_size)
+        out = out.to(linear.weight.device)
+        with torch.no_grad():
+            out.weight.copy_(linear.weight.to(torch.bfloat16))
+            if linear.bias is not None:
+                out.bias.copy_(linear.bias.to(torch.bfloat16))
+        out.weight.requires_grad_(linear.weight.requires_grad)
+        out.train(linear.training)
+        return out
+
+    def extra_repr(self) -> str:
+        return (f"in_features={self.in_features}, out_features={self.out_features}, "
+                f"bias={self.bias is not None}, format=nvfp4")
+
+
+class NVFP4InferenceConfig:
+    """Stands where the reference passes torchao's config of the same name to ``quantize_``
+    (fx/src/s4/models/wan22/wan_loader.py:613-616): which linears to convert."""
+
+    def __init__(self, min_features: int = 32, skip: tuple = ()):
+        self.min_features = min_features
+        self.skip = tuple(skip)          # substrings of module paths to leave alone
+
+    def wants(self, name: str, module: nn.Module) -> bool:
+        return (type(module) is nn.Linear and module.in_features % 32 == 0
+                and module.out_features % 8 == 0
+                and min(module.in_features, module.out_features) >= self.min_features
+                and not any(s in name for s in self.skip))
+
+
+def quantize_(model: nn.Module, config: Optional[NVFP4InferenceConfig] = None, filter_fn=None) -> nn.Module:
+    """In place, replace every ``nn.Linear`` the config wants (and ``filter_fn(module, name)``
+    accepts, when given) by an :class:`NVFP4Linear` with the same weights -- the call shape of
+    ``torchao.quantization.quantize_`` as the reference uses it on the DiT
+    (wan_loader.py:613-616).  Linears whose sizes the GEMM cannot take stay as they are.
+    Returns the model."""
+    config = config or NVFP4InferenceConfig()
+
+    def walk(parent: nn.Module, prefix: str) -> None:
+        for child_name, child in list(parent.named_children()):
+            path = f"{prefix}.{child_name}" if prefix else child_name
+            if config.wants(path, child) and (filter_fn is None or filter_fn(child, path)):
+                setattr(parent, child_name, NVFP4Linear.from_linear(child))
+            else:
+                walk(child, path)
+
+    if config.wants("", model) and (filter_fn is None or filter_fn(model, "")):
+        return NVFP4Linear.from_linear(model)
+    walk(model, "")
+    return model
