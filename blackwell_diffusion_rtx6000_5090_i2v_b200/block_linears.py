@@ -152,3 +152,60 @@ class WanBlockLinears:
         with torch.cuda.graph(graph):
             self.step(inputs)
         return graph
+
+
+class HostStagedLinears:
+    """The block's linears for activations that live in pinned HOST memory: copy in, compute,
+    copy out, on three streams so that the PCIe transfers of one linear overlap the kernels of
+    another and the two directions run at the same time.
+
+    Per linear i:  H2D_i (copy-in stream) -> amax + quantize + GEMM_i (compute stream)
+    -> D2H_i (copy-out stream), chained by events.  From one step to the next, H2D_i waits for
+    the previous GEMM_i to have consumed the device input buffer and GEMM_i waits for the
+    previous D2H_i to have drained the output buffer, so steps can be enqueued back to back.
+    """
+
+    def __init__(self, runner: WanBlockLinears):
+        self.r = runner
+        dev = runner.device
+        self.s_in = torch.cuda.Stream(device=dev)
+        self.s_run = torch.cuda.Stream(device=dev)
+        self.s_out = torch.cuda.Stream(device=dev)
+        self.dev_in = {s.name: torch.empty(runner.tokens, s.k, dtype=torch.bfloat16, device=dev)
+                       for s in runner.specs}
+        mk = lambda: {s.name: torch.cuda.Event() for s in runner.specs}  # noqa: E731
+        self.loaded, self.computed, self.drained = mk(), mk(), mk()
+        self._first = True
+
+    def step(self, host_in: Dict[str, torch.Tensor], host_out: Dict[str, torch.Tensor]) -> None:
+        """Enqueue one pass: ``host_in[name]`` bf16 ``[tokens, k]`` pinned -> ``host_out[name]``
+        bf16 ``[tokens, n]`` pinned.  Returns at once; :meth:`wait` orders the caller's stream
+        after everything enqueued so far."""
+        r = self.r
+        if self._first:
+            cur = torch.cuda.current_stream(r.device)
+            for s in (self.s_in, self.s_run, self.s_out):
+                s.wait_stream(cur)
+        for spec in r.specs:
+            n = spec.name
+            with torch.cuda.stream(self.s_in):
+                if not self._first:
+                    self.s_in.wait_event(self.computed[n])      # input buffer consumed
+                self.dev_in[n].copy_(host_in[n], non_blocking=True)
+                self.loaded[n].record(self.s_in)
+            with torch.cuda.stream(self.s_run):
+                self.s_run.wait_event(self.loaded[n])
+                if not self._first:
+                    self.s_run.wait_event(self.drained[n])      # output buffer copied out
+                y = r.linear(n, self.dev_in[n])
+                self.computed[n].record(self.s_run)
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(self.computed[n])
+                host_out[n].copy_(y, non_blocking=True)
+                self.drained[n].record(self.s_out)
+        self._first = False
+
+    def wait(self) -> None:
+        cur = torch.cuda.current_stream(self.r.device)
+        for s in (self.s_in, self.s_run, self.s_out):
+            cur.wait_stream(s)

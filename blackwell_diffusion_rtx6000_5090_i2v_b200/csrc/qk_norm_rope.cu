@@ -11,9 +11,10 @@
 // tensor can be carried along untouched so that q, k and v land in one packed
 // [tokens, heads, 3 * head_dim] buffer ready for a head/sequence exchange.
 //
-// Layout of the work is that of the fused norm + quantize kernel: a thread owns the same 16
-// columns of every row (its gains stay in registers), a CTA walks over groups of kR tokens
-// that bulk copies stage in a ring of shared-memory slots, one CTA-wide reduction per group.
+// Layout of the work follows the fused norm + quantize kernel: a thread owns the same columns
+// of every row (two 8-element chunks half a CTA apart; its gains stay in registers), a CTA
+// walks over groups of kR tokens that bulk copies stage in a ring of shared-memory slots, one
+// CTA-wide reduction per group.
 // blockIdx.y selects the tensor: 0 = q, 1 = k, 2 = v (copy only).
 #include "nvfp4_common.cuh"
 
@@ -101,7 +102,6 @@ qk_norm_rope_kernel(const RopeArgs p) {
   const int which = blockIdx.y;                             // 0 q, 1 k, 2 v
   const int T = blockDim.x;
   const int warps = T >> 5;
-  const int units = p.dim >> 4;                             // 16-element pieces per row
   const uint32_t row_bytes = (uint32_t)p.dim * 2u;
   const uint32_t slot_bytes = row_bytes * kR;
   const int64_t groups = (p.rows + kR - 1) / kR;
@@ -135,54 +135,67 @@ qk_norm_rope_kernel(const RopeArgs p) {
     }
   }
 
-  // this thread's 16 columns: head, offset in the head, gains
-  const int u = threadIdx.x;
-  const bool live = u < units;
-  const int col = live ? u * 16 : 0;
-  const int head = col / p.head_dim;
-  const int d0 = col - head * p.head_dim;
-  int64_t out_off = (int64_t)head * p.out_head_bytes + (int64_t)d0 * 2;
-  if (p.heads_per_rank > 0) {
-    // plain stores into the owner rank's buffer (its own memory or a peer's over NVLink)
-    const int dst = head / p.heads_per_rank;
+  // This thread's two 8-element chunks of every row: chunk t and chunk t + T, so that a warp's
+  // shared-memory reads and global stores are each one contiguous 512 bytes.  A rotated pair
+  // never straddles a chunk.  Per chunk: head, offset in the head, destination, gains.
+  const int chunks = p.dim >> 3;
+  bool live[2];
+  int d0[2];
+  uint8_t* dst_base[2];
+  int64_t out_off[2];
+  float2 gain[2][4];
 #pragma unroll
-    for (int r = 0; r < 8; ++r)
-      if (r == dst) out = p.peer[r];
-    out_off = p.row_offset * p.out_row_bytes +
-              (int64_t)(head - dst * p.heads_per_rank) * p.out_head_bytes +
-              (int64_t)(which * p.head_dim + d0) * 2;
-  }
-  float2 gain[8];
+  for (int c = 0; c < 2; ++c) {
+    const int ch = threadIdx.x + c * T;
+    live[c] = ch < chunks;
+    const int col = live[c] ? ch * 8 : 0;
+    const int head = col / p.head_dim;
+    d0[c] = col - head * p.head_dim;
+    dst_base[c] = out;
+    out_off[c] = (int64_t)head * p.out_head_bytes + (int64_t)d0[c] * 2;
+    if (p.heads_per_rank > 0) {
+      // plain stores into the owner rank's buffer (its own memory or a peer's over NVLink)
+      const int dst = head / p.heads_per_rank;
 #pragma unroll
-  for (int e = 0; e < 8; ++e) gain[e] = make_float2(1.0f, 1.0f);
-  if (gain_ptr) {
+      for (int r = 0; r < 8; ++r)
+        if (r == dst) dst_base[c] = p.peer[r];
+      out_off[c] = p.row_offset * p.out_row_bytes +
+                   (int64_t)(head - dst * p.heads_per_rank) * p.out_head_bytes +
+                   (int64_t)(which * p.head_dim + d0[c]) * 2;
+    }
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const float4 a = __ldg(reinterpret_cast<const float4*>(gain_ptr + col) + q);
-      gain[2 * q] = make_float2(a.x, a.y);
-      gain[2 * q + 1] = make_float2(a.z, a.w);
+    for (int e = 0; e < 4; ++e) gain[c][e] = make_float2(1.0f, 1.0f);
+    if (gain_ptr) {
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const float4 a = __ldg(reinterpret_cast<const float4*>(gain_ptr + col) + q);
+        gain[c][2 * q] = make_float2(a.x, a.y);
+        gain[c][2 * q + 1] = make_float2(a.z, a.w);
+      }
     }
   }
   const float dim_f = (float)p.dim;
   const int half_hd = p.head_dim >> 1;
+  const bool rotate = which < 2 && p.cos_sin != nullptr;
 
   int slot = 0;
   uint32_t phase = 0;
   int parity = 0;
   for (int64_t g = blockIdx.x; g < groups; g += gridDim.x, parity ^= 1) {
     const int64_t base = g * kR;
-    const bool rotate = which < 2 && p.cos_sin != nullptr;
     wait_group(smem_u32(&full[slot]), phase, &abort_flag, p.status);
     const uint8_t* slot_ptr = ring + (size_t)slot * slot_bytes;
-    uint32_t xp[kR][8];
+    uint32_t xp[kR][2][4];
     bool row_ok[kR];
 #pragma unroll
     for (int r = 0; r < kR; ++r) {
       row_ok[r] = base + r < p.rows;
-      const uint4* src = reinterpret_cast<const uint4*>(slot_ptr + (size_t)r * row_bytes) + 2 * (col >> 4);
-      const uint4 a = src[0], b = src[1];
-      xp[r][0] = a.x; xp[r][1] = a.y; xp[r][2] = a.z; xp[r][3] = a.w;
-      xp[r][4] = b.x; xp[r][5] = b.y; xp[r][6] = b.z; xp[r][7] = b.w;
+      const uint4* src = reinterpret_cast<const uint4*>(slot_ptr + (size_t)r * row_bytes);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const uint4 a = live[c] ? src[threadIdx.x + c * T] : make_uint4(0, 0, 0, 0);
+        xp[r][c][0] = a.x; xp[r][c][1] = a.y; xp[r][c][2] = a.z; xp[r][c][3] = a.w;
+      }
     }
     float rstd[kR];
     if (which < 2) {
@@ -191,11 +204,14 @@ qk_norm_rope_kernel(const RopeArgs p) {
       for (int r = 0; r < kR; ++r) {
         float2 s2 = make_float2(0.0f, 0.0f);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const float2 x = bf16x2_to_f2(xp[r][e]);
-          s2 = f2_fma(x, x, s2);
+        for (int c = 0; c < 2; ++c) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 x = bf16x2_to_f2(xp[r][c][e]);
+            s2 = f2_fma(x, x, s2);
+          }
         }
-        acc[r] = (live && row_ok[r]) ? s2.x + s2.y : 0.0f;
+        acc[r] = row_ok[r] ? s2.x + s2.y : 0.0f;      // chunks past the row hold zeros
       }
       // warp stage: fold the two values across lane bit 4, finish over the other bits
       {
@@ -223,7 +239,7 @@ qk_norm_rope_kernel(const RopeArgs p) {
     } else {
       __syncthreads();
     }
-    // every thread holds its piece: the slot can take the group kStages ahead
+    // every thread holds its chunks: the slot can take the group kStages ahead
     {
       const int64_t gn = g + (int64_t)kStages * gridDim.x;
       if (threadIdx.x == 0 && gn < groups) issue(gn, slot);
@@ -231,42 +247,44 @@ qk_norm_rope_kernel(const RopeArgs p) {
 
 #pragma unroll
     for (int r = 0; r < kR; ++r) {
-      if (!(live && row_ok[r])) continue;
-      uint32_t o[8];
-      // this token's rotation table entries (L1 / L2 hits: every head of the token reads the
-      // same 512 bytes); loaded here rather than ahead of the wait to keep registers, and with
-      // them the number of resident CTAs, in check
-      float4 cs[4];
-      if (rotate) {
-        const float4* t = reinterpret_cast<const float4*>(p.cos_sin + (base + r) * half_hd + (d0 >> 1));
+      if (!row_ok[r]) continue;
+      const float2 r2 = make_float2(rstd[r], rstd[r]);
+      const float2 sign = make_float2(-1.0f, 1.0f);
 #pragma unroll
-        for (int q = 0; q < 4; ++q) cs[q] = __ldg(t + q);
-      }
-      if (which < 2) {
-        const float2 r2 = make_float2(rstd[r], rstd[r]);
-        const float2 sign = make_float2(-1.0f, 1.0f);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          // normalized pair, rounded to bf16 as the unfused model rounds it
-          const uint32_t nb = f2_to_bf16x2(f2_mul(f2_mul(bf16x2_to_f2(xp[r][e]), r2), gain[e]));
-          if (!rotate) {
-            o[e] = nb;
-            continue;
+      for (int c = 0; c < 2; ++c) {
+        if (!live[c]) continue;
+        uint32_t o[4];
+        if (which < 2) {
+          // this token's rotation table entries for the chunk's four pairs (L1 / L2 hits: every
+          // head of the token reads the same 512 bytes)
+          float4 cs[2];
+          if (rotate) {
+            const float4* t = reinterpret_cast<const float4*>(p.cos_sin + (base + r) * half_hd + (d0[c] >> 1));
+            cs[0] = __ldg(t);
+            cs[1] = __ldg(t + 1);
           }
-          const float2 n = bf16x2_to_f2(nb);
-          const float4 t4 = cs[e >> 1];
-          const float c = (e & 1) ? t4.z : t4.x, s = (e & 1) ? t4.w : t4.y;
-          const float2 nc = f2_mul(n, make_float2(c, c));                      // (x1 c, x2 c)
-          const float2 ns = f2_mul(make_float2(n.y, n.x), make_float2(s, s));  // (x2 s, x1 s)
-          o[e] = f2_to_bf16x2(f2_fma(ns, sign, nc));     // (x1 c - x2 s, x2 c + x1 s), +-1 exact
-        }
-      } else {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) o[e] = xp[r][e];
+          for (int e = 0; e < 4; ++e) {
+            // normalized pair, rounded to bf16 as the unfused model rounds it
+            const uint32_t nb = f2_to_bf16x2(f2_mul(f2_mul(bf16x2_to_f2(xp[r][c][e]), r2), gain[c][e]));
+            if (!rotate) {
+              o[e] = nb;
+              continue;
+            }
+            const float2 n = bf16x2_to_f2(nb);
+            const float4 t4 = cs[e >> 1];
+            const float cc = (e & 1) ? t4.z : t4.x, ss = (e & 1) ? t4.w : t4.y;
+            const float2 nc = f2_mul(n, make_float2(cc, cc));                      // (x1 c, x2 c)
+            const float2 ns = f2_mul(make_float2(n.y, n.x), make_float2(ss, ss));  // (x2 s, x1 s)
+            o[e] = f2_to_bf16x2(f2_fma(ns, sign, nc));   // (x1 c - x2 s, x2 c + x1 s), +-1 exact
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) o[e] = xp[r][c][e];
+        }
+        *reinterpret_cast<uint4*>(dst_base[c] + (base + r) * p.out_row_bytes + out_off[c]) =
+            make_uint4(o[0], o[1], o[2], o[3]);
       }
-      uint4* dst = reinterpret_cast<uint4*>(out + (base + r) * p.out_row_bytes + out_off);
-      dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-      dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
     }
     if (++slot == kStages) {
       slot = 0;

@@ -56,3 +56,24 @@ def test_graph_replay_equals_eager():
     ref = nvfp4.fp4_gemm(nvfp4.FP4Tensor.from_bfloat16(inputs["qkv"]),
                          nvfp4.FP4Tensor.from_bfloat16(weights["qkv"]), bias=biases["qkv"])
     assert torch.equal(runner.out["qkv"], ref)
+
+
+def test_host_staged_steps_equal_direct_calls():
+    from blackwell_diffusion_rtx6000_5090_i2v_b200 import nvfp4
+    bl, runner, inputs, weights, biases = _runner(tokens=333)
+    specs = runner.specs
+    host_in = {s.name: torch.empty(333, s.k, dtype=torch.bfloat16).pin_memory() for s in specs}
+    host_out = {s.name: torch.empty(333, s.n, dtype=torch.bfloat16).pin_memory() for s in specs}
+    staged = bl.HostStagedLinears(runner)
+    for rnd in range(3):                      # back-to-back steps reuse the device buffers
+        for i, s in enumerate(specs):
+            host_in[s.name].copy_(student_t_bf16((333, s.k), 100 * rnd + i))
+        staged.step(host_in, host_out)
+        staged.wait()
+        torch.cuda.synchronize()
+        for s in specs:
+            ref = nvfp4.fp4_gemm(nvfp4.FP4Tensor.from_bfloat16(host_in[s.name].cuda()),
+                                 nvfp4.FP4Tensor.from_bfloat16(weights[s.name]), bias=biases[s.name],
+                                 gelu=s.gelu)
+            assert torch.equal(host_out[s.name].cuda(), ref), (rnd, s.name)
+    nvfp4.check_status()
