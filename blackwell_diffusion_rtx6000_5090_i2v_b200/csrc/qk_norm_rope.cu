@@ -12,7 +12,7 @@
 // [tokens, heads, 3 * head_dim] buffer ready for a head/sequence exchange.
 //
 // Layout of the work follows the fused norm + quantize kernel: a thread owns the same columns
-// of every row (two 8-element chunks half a CTA apart; its gains stay in registers), a CTA
+// of every row (kC 8-element chunks a CTA width apart; its gains stay in registers), a CTA
 // walks over groups of kR tokens that bulk copies stage in a ring of shared-memory slots, one
 // CTA-wide reduction per group.
 // blockIdx.y selects the tensor: 0 = q, 1 = k, 2 = v (copy only).
@@ -25,6 +25,10 @@ constexpr int kMaxThreads = 512;
 constexpr int kMaxWarps = kMaxThreads / 32;
 constexpr int kStages = 3;
 constexpr int kR = 2;                              // tokens per group
+#ifndef NVFP4_ROPE_CHUNKS
+#define NVFP4_ROPE_CHUNKS 4
+#endif
+constexpr int kC = NVFP4_ROPE_CHUNKS;              // 8-element chunks per thread and row
 constexpr long long kWaitCycles = 4000000000LL;    // about two seconds; then give up
 constexpr int kErrCopyTimeout = 0xA00;             // status code: a token group never arrived
 
@@ -135,17 +139,17 @@ qk_norm_rope_kernel(const RopeArgs p) {
     }
   }
 
-  // This thread's two 8-element chunks of every row: chunk t and chunk t + T, so that a warp's
+  // This thread's kC 8-element chunks of every row: chunks t, t + T, ..., so that a warp's
   // shared-memory reads and global stores are each one contiguous 512 bytes.  A rotated pair
   // never straddles a chunk.  Per chunk: head, offset in the head, destination, gains.
   const int chunks = p.dim >> 3;
-  bool live[2];
-  int d0[2];
-  uint8_t* dst_base[2];
-  int64_t out_off[2];
-  float2 gain[2][4];
+  bool live[kC];
+  int d0[kC];
+  uint8_t* dst_base[kC];
+  int64_t out_off[kC];
+  float2 gain[kC][4];
 #pragma unroll
-  for (int c = 0; c < 2; ++c) {
+  for (int c = 0; c < kC; ++c) {
     const int ch = threadIdx.x + c * T;
     live[c] = ch < chunks;
     const int col = live[c] ? ch * 8 : 0;
@@ -185,14 +189,14 @@ qk_norm_rope_kernel(const RopeArgs p) {
     const int64_t base = g * kR;
     wait_group(smem_u32(&full[slot]), phase, &abort_flag, p.status);
     const uint8_t* slot_ptr = ring + (size_t)slot * slot_bytes;
-    uint32_t xp[kR][2][4];
+    uint32_t xp[kR][kC][4];
     bool row_ok[kR];
 #pragma unroll
     for (int r = 0; r < kR; ++r) {
       row_ok[r] = base + r < p.rows;
       const uint4* src = reinterpret_cast<const uint4*>(slot_ptr + (size_t)r * row_bytes);
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < kC; ++c) {
         const uint4 a = live[c] ? src[threadIdx.x + c * T] : make_uint4(0, 0, 0, 0);
         xp[r][c][0] = a.x; xp[r][c][1] = a.y; xp[r][c][2] = a.z; xp[r][c][3] = a.w;
       }
@@ -204,7 +208,7 @@ qk_norm_rope_kernel(const RopeArgs p) {
       for (int r = 0; r < kR; ++r) {
         float2 s2 = make_float2(0.0f, 0.0f);
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
+        for (int c = 0; c < kC; ++c) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const float2 x = bf16x2_to_f2(xp[r][c][e]);
@@ -251,7 +255,7 @@ qk_norm_rope_kernel(const RopeArgs p) {
       const float2 r2 = make_float2(rstd[r], rstd[r]);
       const float2 sign = make_float2(-1.0f, 1.0f);
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < kC; ++c) {
         if (!live[c]) continue;
         uint32_t o[4];
         if (which < 2) {
@@ -301,7 +305,7 @@ qk_norm_rope_kernel(const RopeArgs p) {
 }
 
 int launch_rope(RopeArgs& a, int tensors, cudaStream_t st) {
-  const int threads = (a.dim / 16 + 31) / 32 * 32;
+  const int threads = (a.dim / (8 * kC) + 31) / 32 * 32;
   const size_t smem = (size_t)kStages * kR * a.dim * 2;
   if (cudaFuncSetAttribute(qk_norm_rope_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            (int)smem) != cudaSuccess)
@@ -330,7 +334,7 @@ extern "C" NVFP4_API int nvfp4_qk_norm_rope_bf16(const void* q_in, const void* k
                                        int64_t out_row_stride, int64_t out_head_stride,
                                        int* status_dev, void* stream) {
   const int64_t dim = (int64_t)heads * head_dim;
-  if (rows < 0 || heads <= 0 || head_dim <= 0 || head_dim % 16 != 0 || dim > 16 * kMaxThreads ||
+  if (rows < 0 || heads <= 0 || head_dim <= 0 || head_dim % 16 != 0 || dim > 8 * kC * kMaxThreads ||
       in_row_stride < dim || out_head_stride < head_dim || in_row_stride % 8 != 0 ||
       out_row_stride % 8 != 0 || out_head_stride % 8 != 0)
     return NVFP4_ERR_BAD_ARG;
@@ -372,7 +376,7 @@ extern "C" NVFP4_API int nvfp4_qk_norm_rope_exchange_bf16(
     const float* cos_sin, void* const* rank_buffers, int world, int64_t row_offset,
     int* status_dev, void* stream) {
   const int64_t dim = (int64_t)heads * head_dim;
-  if (rows < 0 || heads <= 0 || head_dim <= 0 || head_dim % 16 != 0 || dim > 16 * kMaxThreads ||
+  if (rows < 0 || heads <= 0 || head_dim <= 0 || head_dim % 16 != 0 || dim > 8 * kC * kMaxThreads ||
       in_row_stride < dim || in_row_stride % 8 != 0 || world < 1 || world > 8 ||
       heads % world != 0 || row_offset < 0 || !rank_buffers)
     return NVFP4_ERR_BAD_ARG;
