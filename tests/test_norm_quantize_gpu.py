@@ -32,6 +32,9 @@ def _torch_chain(x, weight, bias, scale, shift, rms, eps):
     (129, 5120, False, True, False),     # norm2 (affine, no modulation), 14B width
     (64, 14336, True, True, True),       # widest row held in registers
     (33, 48, True, False, False),        # a row shorter than one warp pass
+    (17, 3088, False, False, True),      # odd number of scale blocks per row: one block per thread
+    (5, 16384, False, True, True),       # the widest supported row, all four vectors
+    (2049, 1024, True, False, True),     # many short rows, ragged last group
 ])
 def test_fused_norm_quantize(oracle, rows, cols, rms, affine, mod):
     from blackwell_diffusion_rtx6000_5090_i2v_b200 import nvfp4 as nv
