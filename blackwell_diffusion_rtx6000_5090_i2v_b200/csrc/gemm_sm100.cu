@@ -494,6 +494,20 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll 1
       for (int gj = 0; gj < 2; ++gj) {
         const int gi = g_first + gj;
+        // The residual tile's 16-byte pieces (one row per lane, row stride N) are asked for
+        // before anything waits: loaded at their point of use they put sixteen exposed
+        // global-memory latencies per tile on this warp, which made a K = 3072 GEMM with a
+        // residual epilogue-bound (half speed).
+        uint4 cpre[8];
+        {
+          const int cgp = buf ? gi : (gi + kGroups - 1) % kGroups;
+          const int colp = nt * BN + cgp * 64;
+          const __nv_bfloat16* cr = (p.c && row < p.M) ? p.c + (size_t)row * p.N + colp : nullptr;
+#pragma unroll
+          for (int g = 0; g < 8; ++g)
+            cpre[g] = (cr && colp + g * 8 < p.N) ? __ldg(reinterpret_cast<const uint4*>(cr + g * 8))
+                                                 : make_uint4(0, 0, 0, 0);
+        }
         // (the scheduler's other epilogue warp covers this load's latency)
         load_group(gi, x);
         tc_wait_ld();
@@ -543,8 +557,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
             v[4] *= g1.x; v[5] *= g1.y; v[6] *= g1.z; v[7] *= g1.w;
           }
           if (crow && col0 + g * 8 < p.N) {
-            const uint4 cc = __ldg(reinterpret_cast<const uint4*>(crow + g * 8));
-            const uint32_t cw[4] = {cc.x, cc.y, cc.z, cc.w};
+            const uint32_t cw[4] = {cpre[g].x, cpre[g].y, cpre[g].z, cpre[g].w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               v[2 * e] += p.beta * bf16lo_to_f32(cw[e]);

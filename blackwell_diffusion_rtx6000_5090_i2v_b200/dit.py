@@ -365,16 +365,16 @@ class WanBlock:
             a = FP4Tensor.from_norm_mod(x, scale=scale_msa, shift=shift_msa, eps=cfg.eps)
             _mark("norm_quantize")
             qkv = self.qkv.nvfp4(a)
-            _mark("gemm")
+            _mark("gemm_qkv")
             o = self._self_attention_fused(qkv, cos_sin, group, px)
             oq = FP4Tensor.from_bfloat16(o.contiguous(), linear_scales=False)
             _mark("quantize")
             x = self.attn_out.nvfp4(oq, gate=gate_msa, C=x, beta=1.0)
-            _mark("gemm")
+            _mark("gemm_attn_out")
             a = FP4Tensor.from_norm_mod(x, weight=self.norm2_w, bias=self.norm2_b, eps=cfg.eps)
             _mark("norm_quantize")
             q = self.cross_q.nvfp4(a)
-            _mark("gemm")
+            _mark("gemm_cross_q")
             q = rms_norm_fused(q, cfg.heads, cfg.head_dim, self.g_cq, cfg.eps)
             _mark("qk_norm_rope")
             ck, cv = self._cross_kv(ctx, mode)
@@ -384,15 +384,15 @@ class WanBlock:
             oq = FP4Tensor.from_bfloat16(o.contiguous(), linear_scales=False)
             _mark("quantize")
             x = self.cross_out.nvfp4(oq, C=x, beta=1.0)
-            _mark("gemm")
+            _mark("gemm_cross_out")
             a = FP4Tensor.from_norm_mod(x, scale=c_scale, shift=c_shift, eps=cfg.eps)
             _mark("norm_quantize")
             hid = self.ffn_up.nvfp4(a, gelu=True, out_amax=self._amax)
-            _mark("gemm")
+            _mark("gemm_ffn_up")
             hq = FP4Tensor.from_bfloat16(hid, linear_scales=False, amax=self._amax)
             _mark("quantize")
             x = self.ffn_down.nvfp4(hq, gate=c_gate, C=x, beta=1.0)
-            _mark("gemm")
+            _mark("gemm_ffn_down")
             return x
         # comparison path: same ops, linears by dequantize-then-matmul
         ro = mode == "dequant_reordered"

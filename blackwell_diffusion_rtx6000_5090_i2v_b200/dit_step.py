@@ -131,7 +131,15 @@ def main(argv=None) -> int:
         ms = statistics.median(times)
         lin = model.linear_flops(tokens)
         att = model.attention_flops(tokens)
-        gemm_ms = parts.get("gemm", 0.0) + parts.get("text_kv", 0.0)
+        gemm_ms = sum(v for k, v in parts.items() if k.startswith("gemm")) + parts.get("text_kv", 0.0)
+        cfgm, nb = model.cfg, len(model.blocks)
+        per_linear = {}
+        for name, n_out, k_in in (("qkv", 3 * cfgm.dim, cfgm.dim), ("attn_out", cfgm.dim, cfgm.dim),
+                                  ("cross_q", cfgm.dim, cfgm.dim), ("cross_out", cfgm.dim, cfgm.dim),
+                                  ("ffn_up", cfgm.ffn, cfgm.dim), ("ffn_down", cfgm.dim, cfgm.ffn)):
+            ms_l = parts.get("gemm_" + name)
+            if ms_l:
+                per_linear[name] = round(2.0 * (tokens // world) * n_out * k_in * nb / (ms_l * 1e-3) / 1e12, 1)
         line = {
             "metric": "dit_step_latency", "unit": "ms", "value": round(ms, 3),
             "higher_is_better": False, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -144,6 +152,7 @@ def main(argv=None) -> int:
             "components_ms_rank0": {k: round(v, 3) for k, v in sorted(parts.items())},
             "linear_tflop": round(lin / 1e12, 2), "attention_tflop": round(att / 1e12, 2),
             "gemm_tflops_per_gpu": round(lin / world / (gemm_ms * 1e-3) / 1e12, 1) if gemm_ms else None,
+            "gemm_tflops_per_linear_rank0": per_linear,
             "data": "synthetic", "dtype": "nvfp4 linears, bf16 attention",
         }
         line.update(checks)
