@@ -268,6 +268,21 @@ __device__ __forceinline__ float gelu_tanh(float x) {
   return x * r;
 }
 
+// The same on a pair of lanes (the polynomial as f32x2 ops in the scalar form's order; the two
+// special-function ops stay per lane).
+__device__ __forceinline__ float2 gelu_tanh2(float2 x) {
+  const float2 c1 = make_float2(-2.302208198144325f, -2.302208198144325f);
+  const float2 c2 = make_float2(-0.1029432395800235f, -0.1029432395800235f);
+  const float2 z = f2_mul(x, f2_fma(f2_mul(c2, x), x, c1));   // -2 u log2(e)
+  float ex, ey, rx, ry;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ex) : "f"(z.x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ey) : "f"(z.y));
+  const float2 d = f2_add(make_float2(ex, ey), make_float2(1.0f, 1.0f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rx) : "f"(d.x));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(ry) : "f"(d.y));
+  return f2_mul(x, make_float2(rx, ry));
+}
+
 // Tile order.  Tiles are numbered so that the pairs running at one time (consecutive
 // numbers) cover a block of kRasterM tile rows by several tile columns: each A row block is
 // then swept over all columns while it is hot in L2 instead of once per column with the whole
@@ -465,7 +480,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     const uint32_t lead_acc_empty = mapa_u32(acc_empty_bar, 0);
     const uint32_t on = elect_one();
     const uint64_t stream_out = l2_policy_evict_first();
-    __nv_bfloat162 amax2 = __floats2bfloat162_rn(0.0f, 0.0f);   // running max |D| of this thread
+    uint32_t amax2 = 0u;                 // running max |D| of this thread, as a bf16 pair
     uint8_t* slab = smem_gen + kStages * kStageBytes + (warp - 2) * kEpiSlabBytes;
     const int g_first = warp >= 6 ? 2 : 0;   // this warp's groups: g_first, g_first + 1
     bool ok = true;
@@ -533,44 +548,50 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         // the previous store must have finished reading the slab
         asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
         __syncwarp();
+        // Two fp32 lanes per instruction from here to the bf16 pack: at K = 3072 the eight
+        // epilogue warps have about as many issue slots per tile as the main loop has cycles.
+        const float2 scale2 = make_float2(scale, scale);
+        const float2 beta2 = make_float2(p.beta, p.beta);
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
-          float v[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(x[g * 8 + e]) * scale;
+          float2 v[4];
+          const bool in_n = col0 + g * 8 < p.N;
           if (p.bias) {
             const uint32_t bw[4] = {bb[g].x, bb[g].y, bb[g].z, bb[g].w};
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              v[2 * e] += bf16lo_to_f32(bw[e]);
-              v[2 * e + 1] += bf16hi_to_f32(bw[e]);
-            }
+            for (int e = 0; e < 4; ++e)
+              v[e] = f2_fma(make_float2(__uint_as_float(x[g * 8 + 2 * e]),
+                                        __uint_as_float(x[g * 8 + 2 * e + 1])),
+                            scale2, bf16x2_to_f2(bw[e]));
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              v[e] = f2_mul(make_float2(__uint_as_float(x[g * 8 + 2 * e]),
+                                        __uint_as_float(x[g * 8 + 2 * e + 1])), scale2);
           }
           if (p.act == NVFP4_ACT_GELU_TANH) {
 #pragma unroll
-            for (int e = 0; e < 8; ++e) v[e] = gelu_tanh(v[e]);
+            for (int e = 0; e < 4; ++e) v[e] = gelu_tanh2(v[e]);
           }
-          if (p.gate && col0 + g * 8 < p.N) {
+          if (p.gate && in_n) {
             const float4 g0 = __ldg(reinterpret_cast<const float4*>(p.gate + col0 + g * 8));
             const float4 g1 = __ldg(reinterpret_cast<const float4*>(p.gate + col0 + g * 8 + 4));
-            v[0] *= g0.x; v[1] *= g0.y; v[2] *= g0.z; v[3] *= g0.w;
-            v[4] *= g1.x; v[5] *= g1.y; v[6] *= g1.z; v[7] *= g1.w;
+            v[0] = f2_mul(v[0], make_float2(g0.x, g0.y));
+            v[1] = f2_mul(v[1], make_float2(g0.z, g0.w));
+            v[2] = f2_mul(v[2], make_float2(g1.x, g1.y));
+            v[3] = f2_mul(v[3], make_float2(g1.z, g1.w));
           }
-          if (crow && col0 + g * 8 < p.N) {
+          if (crow && in_n) {
             const uint32_t cw[4] = {cpre[g].x, cpre[g].y, cpre[g].z, cpre[g].w};
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              v[2 * e] += p.beta * bf16lo_to_f32(cw[e]);
-              v[2 * e + 1] += p.beta * bf16hi_to_f32(cw[e]);
-            }
+            for (int e = 0; e < 4; ++e) v[e] = f2_fma(beta2, bf16x2_to_f2(cw[e]), v[e]);
           }
           uint32_t o[4];
-          const bool counted = p.d_amax && row < p.M && col0 + g * 8 < p.N;
+          const bool counted = p.d_amax && row < p.M && in_n;
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
-            o[e] = *reinterpret_cast<uint32_t*>(&h);
-            if (counted) amax2 = __hmax2(amax2, __habs2(h));
+            o[e] = f2_to_bf16x2(v[e]);
+            if (counted) amax2 = bf16x2_max_abs(amax2, o[e]);
           }
           // row `lane` of the slab, 16-byte chunk g, at its 128-byte-swizzle position
           *reinterpret_cast<uint4*>(slab + lane * 128 + ((g ^ (lane & 7)) << 4)) =
@@ -588,7 +609,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
     if (p.d_amax) {
       // non-negative floats order like their bit patterns: one atomic per warp per launch
-      const float a = fmaxf(__bfloat162float(amax2.x), __bfloat162float(amax2.y));
+      const float a = fmaxf(bf16lo_to_f32(amax2), bf16hi_to_f32(amax2));
       const unsigned bits = __reduce_max_sync(0xffffffffu, __float_as_uint(a));
       if (lane == 0 && bits != 0u) atomicMax(p.d_amax, bits);
     }
