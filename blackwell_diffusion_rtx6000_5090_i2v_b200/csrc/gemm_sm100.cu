@@ -172,6 +172,17 @@ __device__ __forceinline__ uint64_t l2_policy_evict_first() {
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
   return pol;
 }
+// Tiled load into this CTA's own shared memory, bytes reported to one of its own barriers
+// (the residual tile of the epilogue).  One destination, nothing broadcast.
+__device__ __forceinline__ void tma_load_2d_local(const CUtensorMap* map, uint32_t bar, uint32_t dst,
+                                                  int x, int y, uint64_t policy, uint32_t on) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+      "@q cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      ".L2::cache_hint [%0], [%1, {%3, %4}], [%2], %6;\n\t}"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(on), "l"(policy)
+      : "memory");
+}
 // Tiled store of a shared-memory slab to global memory (clipped at the tensor's edges).
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y,
                                              uint64_t policy, uint32_t on) {
@@ -320,7 +331,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
                   const __grid_constant__ CUtensorMap map_b,
                   const __grid_constant__ CUtensorMap map_sfa,
                   const __grid_constant__ CUtensorMap map_sfb,
-                  const __grid_constant__ CUtensorMap map_d, const Params p) {
+                  const __grid_constant__ CUtensorMap map_d,
+                  const __grid_constant__ CUtensorMap map_c, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -337,7 +349,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
   auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };         // local: the stage's MMAs are done
   auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * kStages + b); };  // local
   const uint32_t acc_empty_bar = bar_base + 8u * (2 * kStages + 2);              // leader
-  static_assert(8 * (2 * kStages + 3) <= 248, "barriers overrun their area");
+  auto c_bar = [&](int w) { return bar_base + 8u * (2 * kStages + 3 + w); };     // local: epilogue warp w's residual tile landed
+  static_assert(8 * (2 * kStages + 3 + kEpiWarps) <= 248, "barriers overrun their area");
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -354,6 +367,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     mbar_init(acc_full_bar(0), 1);
     mbar_init(acc_full_bar(1), 1);
     mbar_init(acc_empty_bar, 2 * 4);  // one arrival per warp that drains the shared columns
+    for (int w = 0; w < kEpiWarps; ++w) mbar_init(c_bar(w), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -484,6 +498,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     uint8_t* slab = smem_gen + kStages * kStageBytes + (warp - 2) * kEpiSlabBytes;
     const int g_first = warp >= 6 ? 2 : 0;   // this warp's groups: g_first, g_first + 1
     bool ok = true;
+    uint32_t c_phase = 0;                // parity of this warp's residual-tile barrier
     int t = 0;
     for (int tile = pair; ok && tile < total_tiles; tile += num_pairs, ++t) {
       int mt, nt;
@@ -509,19 +524,18 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll 1
       for (int gj = 0; gj < 2; ++gj) {
         const int gi = g_first + gj;
-        // The residual tile's 16-byte pieces (one row per lane, row stride N) are asked for
-        // before anything waits: loaded at their point of use they put sixteen exposed
-        // global-memory latencies per tile on this warp, which made a K = 3072 GEMM with a
-        // residual epilogue-bound (half speed).
-        uint4 cpre[8];
-        {
-          const int cgp = buf ? gi : (gi + kGroups - 1) % kGroups;
-          const int colp = nt * BN + cgp * 64;
-          const __nv_bfloat16* cr = (p.c && row < p.M) ? p.c + (size_t)row * p.N + colp : nullptr;
-#pragma unroll
-          for (int g = 0; g < 8; ++g)
-            cpre[g] = (cr && colp + g * 8 < p.N) ? __ldg(reinterpret_cast<const uint4*>(cr + g * 8))
-                                                 : make_uint4(0, 0, 0, 0);
+        const int cg = buf ? gi : (gi + kGroups - 1) % kGroups;
+        const int col0 = nt * BN + cg * 64;
+        // The residual tile (32 rows x 64 columns of C) comes into the slab by one TMA load, in
+        // the layout the result will leave in, while tensor memory is being read: as per-lane
+        // row-strided 16-byte loads it put sixteen exposed global-memory latencies per tile on
+        // this warp and made a K = 3072 GEMM with a residual epilogue-bound (half speed).
+        if (p.c) {
+          // the previous store must have finished reading the slab
+          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          __syncwarp();
+          mbar_expect_tx(c_bar(warp - 2), kEpiSlabBytes, on);
+          tma_load_2d_local(&map_c, c_bar(warp - 2), smem_u32(slab), col0, row0, stream_out, on);
         }
         // (the scheduler's other epilogue warp covers this load's latency)
         load_group(gi, x);
@@ -532,8 +546,6 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(lead_acc_empty);
         }
-        const int cg = buf ? gi : (gi + kGroups - 1) % kGroups;
-        const int col0 = nt * BN + cg * 64;
         // per-column operands of the whole group first, so that their loads overlap
         uint4 bb[8];
         if (p.bias) {
@@ -543,11 +555,16 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
                         ? __ldg(reinterpret_cast<const uint4*>(p.bias + col0 + g * 8))
                         : make_uint4(0, 0, 0, 0);
         }
-        const __nv_bfloat16* crow =
-            (p.c && row < p.M) ? p.c + (size_t)row * p.N + col0 : nullptr;
-        // the previous store must have finished reading the slab
-        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-        __syncwarp();
+        if (!p.c) {
+          // the previous store must have finished reading the slab
+          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          __syncwarp();
+        } else {
+          ok = mbar_wait(c_bar(warp - 2), c_phase, abort_flag, p.status, 0x800 + (warp - 2));
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          c_phase ^= 1u;
+        }
         // Two fp32 lanes per instruction from here to the bf16 pack: at K = 3072 the eight
         // epilogue warps have about as many issue slots per tile as the main loop has cycles.
         const float2 scale2 = make_float2(scale, scale);
@@ -581,8 +598,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
             v[2] = f2_mul(v[2], make_float2(g1.x, g1.y));
             v[3] = f2_mul(v[3], make_float2(g1.z, g1.w));
           }
-          if (crow && in_n) {
-            const uint32_t cw[4] = {cpre[g].x, cpre[g].y, cpre[g].z, cpre[g].w};
+          if (p.c) {   // rows past M and columns past N were zero-filled by the load
+            const uint4 cc = *reinterpret_cast<const uint4*>(slab + lane * 128 + ((g ^ (lane & 7)) << 4));
+            const uint32_t cw[4] = {cc.x, cc.y, cc.z, cc.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) v[e] = f2_fma(beta2, bf16x2_to_f2(cw[e]), v[e]);
           }
@@ -716,13 +734,19 @@ extern "C" int nvfp4_gemm(const uint8_t* a_packed, const uint8_t* b_packed,
   int rc = check_device_sm100();
   if (rc != NVFP4_OK) return rc;
 
-  CUtensorMap map_a, map_b, map_sfa, map_sfb, map_d;
+  CUtensorMap map_a, map_b, map_sfa, map_sfb, map_d, map_c;
   if (!gemm::make_map(&map_a, a_packed, M, K / 2, gemm::BM) ||
       !gemm::make_map(&map_b, b_packed, N, K / 2, gemm::BN / 2) ||
       !gemm::make_sf_map(&map_sfa, a_scales_swizzled, sf_row_tiles(M) * sf_k_atoms(K)) ||
       !gemm::make_sf_map(&map_sfb, b_scales_swizzled, sf_row_tiles(N) * sf_k_atoms(K)) ||
       !gemm::make_d_map(&map_d, d_bf16, M, N))
     return NVFP4_ERR_LAUNCH_FAILED;
+  if (c_bf16) {
+    // same geometry as the output: the epilogue loads residual tiles into its output slabs
+    if (!gemm::make_d_map(&map_c, const_cast<void*>(c_bf16), M, N)) return NVFP4_ERR_LAUNCH_FAILED;
+  } else {
+    map_c = map_d;   // never dereferenced
+  }
 
   gemm::Params p;
   p.sfa = a_scales_swizzled;
@@ -774,7 +798,7 @@ extern "C" int nvfp4_gemm(const uint8_t* a_packed, const uint8_t* b_packed,
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, gemm::nvfp4_gemm_kernel, map_a, map_b, map_sfa, map_sfb, map_d, p) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, gemm::nvfp4_gemm_kernel, map_a, map_b, map_sfa, map_sfb, map_d, map_c, p) != cudaSuccess) {
     cudaGetLastError();
     return NVFP4_ERR_LAUNCH_FAILED;
   }

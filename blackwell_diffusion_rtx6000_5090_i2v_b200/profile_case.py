@@ -40,6 +40,8 @@ def main():
     ap.add_argument("--k", type=int, default=3072)
     ap.add_argument("--gelu", action="store_true")
     ap.add_argument("--bias", action="store_true")
+    ap.add_argument("--gate", action="store_true", help="per-column fp32 gate in the epilogue")
+    ap.add_argument("--residual", action="store_true", help="+ C (bf16 [m, n]) in the epilogue")
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--iters", type=int, default=3)
     a = ap.parse_args()
@@ -52,7 +54,10 @@ def main():
         qb = FP4Tensor.from_bfloat16(w, linear_scales=False)
         out = torch.empty(a.m, a.n, dtype=torch.bfloat16, device="cuda")
         bias = torch.zeros(a.n, dtype=torch.bfloat16, device="cuda") if a.bias else None
-        ms = _time(lambda: fp4_gemm(qa, qb, out=out, gelu=a.gelu, bias=bias), a.warmup, a.iters)
+        gate = torch.ones(a.n, dtype=torch.float32, device="cuda") if a.gate else None
+        res = student_t_bf16((a.m, a.n), 9, device="cuda") if a.residual else None
+        ms = _time(lambda: fp4_gemm(qa, qb, 1.0, 1.0 if a.residual else 0.0, out=out, gelu=a.gelu,
+                                    bias=bias, gate=gate, C=res), a.warmup, a.iters)
         N.check_status()
         print(f"gemm M={a.m} N={a.n} K={a.k}: {ms:.4f} ms, "
               f"{2.0 * a.m * a.n * a.k / ms / 1e9:.1f} TFLOP/s")

@@ -251,3 +251,25 @@ def test_output_amax_fused_in_epilogue(nv):
     assert float(amax.item()) == float(y.abs().max().float().item())
     q = nv.FP4Tensor.from_bfloat16(y)
     assert float(q.global_amax().item()) == float(amax.item())
+
+
+def test_residual_tiles_land_where_they_belong(nv, oracle):
+    """Residual with ragged M and N over several tiles: the epilogue fetches each 32 x 64 piece
+    of C by a tiled copy into the output slab, so a misplaced or mis-swizzled piece shows up per
+    piece, not in the global norm.  The residual is large against the product."""
+    M, N, K = 700, 776, 256
+    x = randn_bf16((M, K), 31)
+    w = randn_bf16((N, K), 32, 0.02)
+    res = randn_bf16((M, N), 33, 4.0)
+    a = nv.FP4Tensor.from_bfloat16(x.cuda())
+    b = nv.FP4Tensor.from_bfloat16(w.cuda())
+    y = nv.fp4_gemm(a, b, 1.0, 1.0, C=res.cuda()).float().cpu()
+    nv.check_status()
+    ref = _oracle_gemm(oracle, x, w, residual=res)
+    assert rel_fro(y, ref) <= TOL
+    for m0 in range(0, M, 32):
+        for n0 in range(0, N, 64):
+            assert rel_fro(y[m0:m0 + 32, n0:n0 + 64], ref[m0:m0 + 32, n0:n0 + 64]) <= 2 * TOL, (m0, n0)
+    # and the plain product is what is left after taking the residual away again
+    plain = nv.fp4_gemm(a, b).float().cpu()
+    assert (y - res.float() - plain).abs().max() <= 0.15        # bf16 rounding at |y| up to 16+
