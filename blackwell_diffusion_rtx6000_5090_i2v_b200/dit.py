@@ -6,12 +6,13 @@ for the block, :389-441 for the step): adaLN-modulated self-attention with q/k
 RMSNorm across heads and 3-D RoPE, cross-attention over the text context, and a
 GELU-tanh feed-forward.  It exists to measure the step latency of the
 benchmark configurations and to check the NVFP4 path end to end, not as a
-model implementation: attention, RoPE and the small embedders are plain bf16
-torch ops.
+model implementation: attention is torch's scaled-dot-product attention in
+bf16 and the small embedders are torch ops.
 
 Two ways of evaluating a linear share the same packed weights:
   * ``nvfp4``   -- fused norm+modulation+quantize, tcgen05 FP4 GEMM with bias /
-                   GELU / gate / residual in its epilogue (the product path);
+                   GELU / gate / residual in its epilogue, fused q/k RMSNorm +
+                   RoPE between the QKV linear and attention (the product path);
   * ``dequant`` -- quantize, dequantize both operands to fp32, fp32 matmul (no
                    TF32), then the same elementwise ops in torch: the
                    dequantize-then-matmul formulation, used as the comparison
