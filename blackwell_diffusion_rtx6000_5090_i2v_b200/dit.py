@@ -512,6 +512,23 @@ class WanDiT:
             y = torch.cat(parts, dim=0)
         return self._unpatchify(y, grid)
 
+    def capture(self, latent: torch.Tensor, t: float, text: torch.Tensor):
+        """Record one single-GPU NVFP4 step into a CUDA graph (the static-shape capture of
+        fx/src/s4/models/wan_22/wan_attention_static.py:566-630).  Returns ``(graph, out)``:
+        ``graph.replay()`` re-runs the step on whatever ``latent`` and ``text`` then contain
+        (same tensors, same timestep) and leaves the result in ``out``.  Everything the step
+        launches is capturable: the library's kernels run on the current stream, never
+        synchronise with the host, and take their temporaries from the torch allocator."""
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            self.forward(latent, t, text)           # warm-up: tables, status word, lazy buffers
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            out = self.forward(latent, t, text)
+        return graph, out
+
     def compare_blocks(self, latent: torch.Tensor, t: float, text: torch.Tensor
                        ) -> List[Tuple[float, float]]:
         """Every block evaluated both ways FROM THE SAME INPUT (the NVFP4 trajectory's): per

@@ -38,6 +38,8 @@ def main(argv=None) -> int:
     ap.add_argument("--warmup", type=int, default=1)
     ap.add_argument("--check", action="store_true", help="cosine against the dequant model")
     ap.add_argument("--sdpa", choices=["default", "flash", "cudnn"], default="default")
+    ap.add_argument("--graph", action="store_true",
+                    help="single GPU: also time the step replayed from a CUDA graph")
     ap.add_argument("--exchange", choices=["nccl", "peer"], default="nccl",
                     help="head/sequence exchange: all-to-alls, or stores into peer memory")
     args = ap.parse_args(argv)
@@ -105,6 +107,19 @@ def main(argv=None) -> int:
         dit.TIMELINE = None
 
         checks = {}
+        if args.graph and world == 1:
+            graph, gout = model.capture(latent, 500.0, text)
+            gtimes = []
+            for _ in range(args.steps):
+                fence()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                graph.replay()
+                e1.record()
+                fence()
+                gtimes.append(e0.elapsed_time(e1))
+            checks["graph_replay_ms"] = round(statistics.median(gtimes), 3)
+            checks["graph_replay_equals_eager"] = bool(torch.equal(gout, y))
         if args.check:
             ref = step(mode="dequant")
             checks["cosine_vs_dequant_model"] = _cos(y, ref)

@@ -161,3 +161,22 @@ def test_fused_rms_norm_only():
     ref = dit.rms_norm(x, gain, 1e-6).view(130, 40, 128)
     assert float((got != ref).float().mean()) < 5e-3
     assert bool(((got.float() - ref.float()).abs() <= 2.0 ** -7 * ref.float().abs()).all())
+
+
+def test_step_replayed_from_a_cuda_graph(small):
+    from blackwell_diffusion_rtx6000_5090_i2v_b200 import nvfp4
+    dit, model, latent, text = small
+    eager = model.forward(latent, 500.0, text)
+    graph, out = model.capture(latent, 500.0, text)
+    out.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    nvfp4.check_status()
+    assert torch.equal(out, eager)
+    # new latent contents in the same tensor are picked up
+    latent2 = torch.randn_like(latent.float()).to(torch.bfloat16)
+    ref2 = model.forward(latent2, 500.0, text)
+    latent.copy_(latent2)
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, ref2)
