@@ -445,11 +445,6 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       const uint32_t sfb_t = tmem_base + kSfCol + 16;   // SFB of K-block j at +8j (two halves)
       for (int tile = pair; ok && tile < total_tiles; tile += num_pairs, ++t) {
         const uint32_t acc = tmem_base + ((t & 1) ? kAccCol1 : 0);
-        if (t > 0) {
-          ok = mbar_wait(acc_empty_bar, (uint32_t)(t - 1) & 1u, abort_flag, p.status, 0x300);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-        }
         for (int kt = 0; kt < p.k_tiles; ++kt) {
           ok = mbar_wait(full_bar(s), ph, abort_flag, p.status, 0x200 + s);
           ok = __all_sync(0xffffffffu, ok);
@@ -463,6 +458,15 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
             tc_cp_sf_pair(sfa_t + 4 * j, desc_sf(sfa_s + j * kSfAtomBytes), on);
             tc_cp_sf_pair(sfb_t + 8 * j, desc_sf(sfb_s + j * kSfAtomBytes), on);
             tc_cp_sf_pair(sfb_t + 8 * j + 4, desc_sf(sfb_s + kSfbBytes / 2 + j * kSfAtomBytes), on);
+          }
+          if (kt == 0 && t > 0) {
+            // Only the MMAs need the previous tile's shared accumulator columns drained; the
+            // scale copies above went ahead of this wait (they follow the previous tile's MMAs
+            // in issue order, which is all the single scale buffer needs).
+            ok = mbar_wait(acc_empty_bar, (uint32_t)(t - 1) & 1u, abort_flag, p.status, 0x300);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
           }
           const uint64_t da = desc_sw128(st);
           const uint64_t db = desc_sw128(st + kABytes);
