@@ -534,6 +534,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         const int gi = g_first + gj;
         const int cg = buf ? gi : (gi + kGroups - 1) % kGroups;
         const int col0 = nt * BN + cg * 64;
+        // tensor-memory loads first (they are asynchronous until the wait below): for the
+        // shared group they sit on the path to the next tile's first MMA
+        load_group(gi, x);
         // The residual tile (32 rows x 64 columns of C) comes into the slab by one TMA load, in
         // the layout the result will leave in, while tensor memory is being read: as per-lane
         // row-strided 16-byte loads it put sixteen exposed global-memory latencies per tile on
@@ -545,8 +548,6 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
           mbar_expect_tx(c_bar(warp - 2), kEpiSlabBytes, on);
           tma_load_2d_local(&map_c, c_bar(warp - 2), smem_u32(slab), col0, row0, stream_out, on);
         }
-        // (the scheduler's other epilogue warp covers this load's latency)
-        load_group(gi, x);
         tc_wait_ld();
         if (gi == 0) {
           // the shared columns are in registers: the issuer may start the next tile
