@@ -122,12 +122,12 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
 }
 // Arrive on a barrier given by its shared::cluster address (this CTA's or the peer's).
-// Relaxed: the only user says "my tensor-memory loads have completed" (tcgen05.wait::ld came
-// first) and publishes no shared or global data through the barrier, so it does not need the
-// cluster-scope release, which on a remote barrier holds the arrival back by on the order of a
-// thousand cycles -- on the critical path between two tiles.
+// Release semantics are required even though no shared or global data is published: with a
+// relaxed arrive the issuer now and then (a few launches in a hundred at M = 27280) started the
+// next tile's MMAs before a CTA's epilogue warps had read the shared accumulator columns --
+// one tile's 128 x 64 piece wrong, found by comparing repeated launches bit for bit.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
-  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)
                : "memory");
 }
 // Bounded wait.  Returns false (after raising the abort flag and recording
