@@ -354,7 +354,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
   auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * kStages + b); };  // local
   const uint32_t acc_empty_bar = bar_base + 8u * (2 * kStages + 2);              // leader
   auto c_bar = [&](int w) { return bar_base + 8u * (2 * kStages + 3 + w); };     // local: epilogue warp w's residual tile landed
-  static_assert(8 * (2 * kStages + 3 + kEpiWarps) <= 248, "barriers overrun their area");
+  // leader: the column groups of accumulator b that do NOT gate the next tile have been read
+  auto acc_rest_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 3 + kEpiWarps + b); };
+  static_assert(8 * (2 * kStages + 3 + kEpiWarps + 2) <= 248, "barriers overrun their area");
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -372,6 +374,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     mbar_init(acc_full_bar(1), 1);
     mbar_init(acc_empty_bar, 2 * 4);  // one arrival per warp that drains the shared columns
     for (int w = 0; w < kEpiWarps; ++w) mbar_init(c_bar(w), 1);
+    mbar_init(acc_rest_bar(0), 2 * 4);   // one arrival per warp that reads the other two groups
+    mbar_init(acc_rest_bar(1), 2 * 4);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -470,6 +474,17 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
             ok = mbar_wait(acc_empty_bar, (uint32_t)(t - 1) & 1u, abort_flag, p.status, 0x300);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
+            if (t >= 2) {
+              // This accumulator was last used two tiles ago.  The warps that own its shared
+              // group have been through it (they arrived above for the tile in between); the
+              // warps that own its other two groups are tracked here.  They are normally a
+              // whole main loop ahead, so this wait costs nothing; without it a short K and a
+              // slow residual load could let these MMAs overwrite columns not yet read.
+              ok = mbar_wait(acc_rest_bar(t & 1), (uint32_t)((t >> 1) - 1) & 1u, abort_flag,
+                             p.status, 0x310);
+              ok = __all_sync(0xffffffffu, ok);
+              if (!ok) break;
+            }
             tc_fence_after();
           }
           const uint64_t da = desc_sw128(st);
@@ -554,6 +569,11 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(lead_acc_empty);
+        } else if (gi == kGroups - 1) {
+          // the last of the other groups is in registers: this accumulator may be reused
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(mapa_u32(acc_rest_bar(buf), 0));
         }
         // per-column operands of the whole group first, so that their loads overlap
         uint4 bb[8];

@@ -290,3 +290,20 @@ def test_repeated_launches_are_bit_identical_at_full_size(nv):
         y = nv.fp4_gemm(a, b, 1.0, 1.0, bias=bias, gate=gate, C=res, out=out)
         assert torch.equal(y, ref), i
     nv.check_status()
+
+
+def test_short_k_many_tiles_repeatable(nv, oracle):
+    """K of one pipeline stage: the main loop of a tile is shorter than its epilogue, the
+    regime in which reuse of an accumulator has to wait for every warp that still reads it."""
+    M, N, K = 4096, 2048, 128
+    x = randn_bf16((M, K), 51)
+    w = randn_bf16((N, K), 52, 0.05)
+    res = randn_bf16((M, N), 53)
+    a = nv.FP4Tensor.from_bfloat16(x.cuda())
+    b = nv.FP4Tensor.from_bfloat16(w.cuda())
+    rc = res.cuda()
+    ref = nv.fp4_gemm(a, b, 1.0, 1.0, C=rc, gelu=True).clone()
+    assert rel_fro(ref.float().cpu(), _oracle_gemm(oracle, x, w, act=1, residual=res)) <= TOL
+    for i in range(100):
+        assert torch.equal(nv.fp4_gemm(a, b, 1.0, 1.0, C=rc, gelu=True), ref), i
+    nv.check_status()
