@@ -770,6 +770,8 @@ extern "C" int nvfp4_gemm(const uint8_t* a_packed, const uint8_t* b_packed,
       !gemm::make_sf_map(&map_sfb, b_scales_swizzled, sf_row_tiles(N) * sf_k_atoms(K)) ||
       !gemm::make_d_map(&map_d, d_bf16, M, N))
     return NVFP4_ERR_LAUNCH_FAILED;
+  // beta == 0 means C is not read at all (BLAS convention): a NaN in it cannot reach D
+  if (beta == 0.0f) c_bf16 = nullptr;
   if (c_bf16) {
     // same geometry as the output: the epilogue loads residual tiles into its output slabs
     if (!gemm::make_d_map(&map_c, const_cast<void*>(c_bf16), M, N)) return NVFP4_ERR_LAUNCH_FAILED;

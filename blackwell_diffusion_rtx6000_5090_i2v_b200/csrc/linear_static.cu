@@ -66,7 +66,12 @@ int nvfp4_linear_bf16_static(const void* x_bf16, int64_t M, int64_t K, const uin
                              int64_t N, const void* bias_bf16, int act, void* y_bf16,
                              int* status_dev, void* stream) {
   if (M < 0 || K < 0 || N < 0 || K % 32 != 0 || N % 8 != 0) return NVFP4_ERR_BAD_ARG;
-  // the fixed scratch bounds the activation; larger problems must use the caller-allocated path
+  // each extent on its own first, so that the products below cannot wrap
+  if (M > kMaxElems || K > kMaxElems || N > (1 << 30)) return NVFP4_ERR_BAD_ARG;
+  // The fixed scratch bounds the activation: M*K elements of nibbles, and the swizzled
+  // scales, whose rows pad to 256 and K to 256 elements (so a very skinny activation can
+  // exceed the scale area well below the element limit).  Larger problems must use the
+  // caller-allocated path.
   if (M * K > kMaxElems || sf_swizzled_bytes(M, K) > kScaleBytes) return NVFP4_ERR_BAD_ARG;
   if (M == 0 || N == 0) return NVFP4_OK;
   if (K == 0 || !x_bf16 || !w_packed || !w_scales_swizzled || !y_bf16) return NVFP4_ERR_BAD_ARG;

@@ -474,7 +474,7 @@ int check_args(const void* x, int64_t rows, int64_t cols) {
     return NVFP4_ERR_BAD_ARG;
   if (rows > 0 && !x) return NVFP4_ERR_BAD_ARG;
   if (!aligned16(x)) return NVFP4_ERR_BAD_ALIGN;
-  return check_device_sm100();
+  return NVFP4_OK;     // the device is checked last: bad arguments are refused on any machine
 }
 
 bool vec_ok(const float* p) { return aligned16(p); }
@@ -497,13 +497,25 @@ int launch_variant(const NormArgs& a, int threads, cudaStream_t st) {
   auto kernel = norm_mod_kernel<kQuantize, kJ, kAffine, kMod>;
   constexpr int kR = RowsPerIter<kJ>::value;
   const size_t smem = (size_t)kStages * kR * a.cols * 2;
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
-      cudaSuccess)
-    return NVFP4_ERR_LAUNCH_FAILED;
-  int per_sm = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem) != cudaSuccess ||
-      per_sm < 1)
-    return NVFP4_ERR_LAUNCH_FAILED;
+  // (dynamic shared memory limit, CTAs per SM) of the last geometry this variant saw on each
+  // device: a model calls it with one row width over and over
+  struct Geometry { size_t smem; int threads; int per_sm; };
+  static Geometry cached[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  Geometry& c = cached[dev];
+  if (c.per_sm < 1 || c.smem != smem || c.threads != threads) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+        cudaSuccess)
+      return NVFP4_ERR_LAUNCH_FAILED;
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, smem) != cudaSuccess ||
+        n < 1)
+      return NVFP4_ERR_LAUNCH_FAILED;
+    c = Geometry{smem, threads, n};
+  }
+  const int per_sm = c.per_sm;
   const int64_t groups = (a.rows + kR - 1) / kR;
   const int64_t resident = (int64_t)sm_count() * per_sm;
   const unsigned grid = (unsigned)(groups < resident ? groups : resident);
@@ -545,6 +557,8 @@ int nvfp4_norm_mod_amax_bf16(const void* x_bf16, int64_t rows, int64_t cols, con
   if (!row_stats || !amax_dev) return NVFP4_ERR_BAD_ARG;
   if (!aligned16(h_out_bf16) || !vec_ok(weight) || !vec_ok(bias) || !vec_ok(scale) || !vec_ok(shift))
     return NVFP4_ERR_BAD_ALIGN;
+  rc = check_device_sm100();
+  if (rc != NVFP4_OK) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(amax_dev, 0, sizeof(float), st) != cudaSuccess) return NVFP4_ERR_LAUNCH_FAILED;
   if (rows == 0) return NVFP4_OK;
@@ -569,9 +583,12 @@ int nvfp4_norm_mod_quantize_bf16(const void* x_bf16, int64_t rows, int64_t cols,
   int rc = check_args(x_bf16, rows, cols);
   if (rc != NVFP4_OK) return rc;
   if (!row_stats || !amax_dev || (rows > 0 && !packed)) return NVFP4_ERR_BAD_ARG;
-  if ((reinterpret_cast<uintptr_t>(packed) & 3u) || !vec_ok(weight) || !vec_ok(bias) ||
+  // the kernel stores 8-byte words of nibbles
+  if ((reinterpret_cast<uintptr_t>(packed) & 7u) || !vec_ok(weight) || !vec_ok(bias) ||
       !vec_ok(scale) || !vec_ok(shift))
     return NVFP4_ERR_BAD_ALIGN;
+  rc = check_device_sm100();
+  if (rc != NVFP4_OK) return rc;
   if (rows == 0) return NVFP4_OK;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (scales_swizzled) {

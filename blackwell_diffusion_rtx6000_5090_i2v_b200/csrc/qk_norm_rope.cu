@@ -305,15 +305,28 @@ qk_norm_rope_kernel(const RopeArgs p) {
 }
 
 int launch_rope(RopeArgs& a, int tensors, cudaStream_t st) {
-  const int threads = (a.dim / (8 * kC) + 31) / 32 * 32;
+  // enough threads for every 8-element chunk of a row, kC chunks per thread, whole warps
+  const int threads = ((a.dim / 8 + kC - 1) / kC + 31) / 32 * 32;
   const size_t smem = (size_t)kStages * kR * a.dim * 2;
-  if (cudaFuncSetAttribute(qk_norm_rope_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           (int)smem) != cudaSuccess)
-    return NVFP4_ERR_LAUNCH_FAILED;
-  int per_sm = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, qk_norm_rope_kernel, threads, smem) !=
-          cudaSuccess || per_sm < 1)
-    return NVFP4_ERR_LAUNCH_FAILED;
+  // (dynamic shared memory limit, CTAs per SM) of the last geometry seen on each device:
+  // the model calls this with one row width over and over
+  struct Geometry { size_t smem; int threads; int per_sm; };
+  static Geometry cached[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  Geometry& c = cached[dev];
+  if (c.per_sm < 1 || c.smem != smem || c.threads != threads) {
+    if (cudaFuncSetAttribute(qk_norm_rope_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess)
+      return NVFP4_ERR_LAUNCH_FAILED;
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, qk_norm_rope_kernel, threads, smem) !=
+            cudaSuccess || n < 1)
+      return NVFP4_ERR_LAUNCH_FAILED;
+    c = Geometry{smem, threads, n};
+  }
+  const int per_sm = c.per_sm;
   const int64_t groups = (a.rows + kR - 1) / kR;
   int64_t gx = ((int64_t)sm_count() * per_sm + tensors - 1) / tensors;
   if (gx > groups) gx = groups;

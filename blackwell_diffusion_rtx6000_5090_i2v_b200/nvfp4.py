@@ -334,6 +334,9 @@ def fp4_gemm(A: FP4Tensor, B: FP4Tensor, alpha: float = 1.0, beta: float = 0.0, 
     fp32 device tensor) receives max|output|, sparing the next quantizer its amax pass."""
     if out_amax is not None and (out_amax.dtype != torch.float32 or out_amax.numel() != 1):
         raise RuntimeError("[s4] [nvfp4] [gemm] out_amax must be a one-element float32 tensor")
+    if C is not None and beta == 0.0:
+        # beta keeps the reference's default of 0, under which a C would be silently ignored
+        raise RuntimeError("[s4] [nvfp4] [gemm] C given with beta == 0: pass the beta to apply")
     return _gemm_packed(A, B, alpha, beta, C, bias, gate, gelu, out, out_amax)
 
 

@@ -30,15 +30,21 @@ _weight_cache: dict = {}
 def quantized_weight(weight: torch.Tensor) -> FP4Tensor:
     """NVFP4 copy of a ``[N, K]`` bf16 weight, reused until the tensor is
     modified in place, reallocated or freed."""
+    try:
+        version = weight._version
+    except RuntimeError:
+        # tensors created under torch.inference_mode() track no version: an in-place change
+        # could not be noticed, so they are quantized on every call
+        return FP4Tensor.from_bfloat16(weight.detach(), linear_scales=False)
     key = id(weight)
     hit = _weight_cache.get(key)
     if hit is not None:
-        ref, version, ptr, q = hit
-        if ref() is weight and version == weight._version and ptr == weight.data_ptr():
+        ref, cached_version, ptr, q = hit
+        if ref() is weight and cached_version == version and ptr == weight.data_ptr():
             return q
     q = FP4Tensor.from_bfloat16(weight.detach(), linear_scales=False)
     _weight_cache[key] = (weakref.ref(weight, lambda _r, k=key: _weight_cache.pop(k, None)),
-                          weight._version, weight.data_ptr(), q)
+                          version, weight.data_ptr(), q)
     return q
 
 

@@ -190,8 +190,10 @@ NVFP4_API int nvfp4_qk_norm_rope_exchange_bf16(const void* q_in, const void* k_i
  * device array inside the library (about 5 MiB, held by every GPU that loads the library
  * until the process exits).  x is bf16 [M, K]; the weight is given pre-quantized (packed
  * [N, K/2], swizzled scales, device tensor scale); y is bf16 [M, N]; bias may be null.
- * Limits: M*K <= nvfp4_linear_bf16_static_max_elements() (8 Mi) and K % 32 == 0, N % 8 == 0;
- * anything larger returns NVFP4_ERR_BAD_ARG.  The first call on each device resolves the
+ * Limits: M*K <= nvfp4_linear_bf16_static_max_elements() (8 Mi), K % 32 == 0, N % 8 == 0, and
+ * the padded scale layout must fit 1 MiB: ceil(M/256) * ceil(K/256) <= 256 (rows pad to 256 and
+ * K to 256 elements, so a very skinny activation such as M = 1, K = 131072 is refused although
+ * it has few elements); anything larger returns NVFP4_ERR_BAD_ARG.  The first call on each device resolves the
  * array's device address (with that device current); make that first call outside any
  * stream capture.  No call allocates.  All calls on a device share the one array: two calls
  * whose kernels can overlap on the GPU (different streams without ordering) race; calls on

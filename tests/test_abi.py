@@ -57,6 +57,13 @@ def test_argument_validation_without_device():
     assert L.nvfp4_gemm(None, None, None, None, None, None, 0, 16, 64, 1.0, 0.0, None, None,
                         None, 0, None, None, None, None) == 0  # empty problem is a no-op
     assert L.nvfp4_amax_bf16(None, 16, None, None) == 1
+    # the fused norm quantizer stores 8-byte words of nibbles: a packed pointer that is only
+    # 4-byte aligned is refused on the host (status 2), nothing is launched
+    fake = 0x10000
+    assert L.nvfp4_norm_mod_quantize_bf16(fake, 4, 64, None, None, None, None, fake, fake, fake + 4,
+                                          None, None, None, None, None) == 2
+    assert L.nvfp4_norm_mod_quantize_bf16(fake + 8, 4, 64, None, None, None, None, fake, fake, fake,
+                                          None, None, None, None, None) == 2   # x itself
 
 
 def test_host_api_mirrors_reference_names():

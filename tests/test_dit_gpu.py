@@ -119,14 +119,18 @@ def test_flop_counts():
     assert abs(m.attention_flops(27280) / 1e12 - 279.5) < 1.0
 
 
-@pytest.mark.parametrize("L,heads,packed", [(301, 4, False), (64, 24, True), (7, 40, False)])
-def test_fused_qk_norm_rope_matches_torch_ops(L, heads, packed):
+@pytest.mark.parametrize("L,heads,packed,D", [
+    (301, 4, False, 128), (64, 24, True, 128), (7, 40, False, 128),
+    (33, 13, False, 80),      # 130 eight-element chunks per row: two past a multiple of 128
+    (9, 65, True, 16),        # the same row width out of 16-wide heads
+])
+def test_fused_qk_norm_rope_matches_torch_ops(L, heads, packed, D):
     """The fused q/k RMSNorm + rotary kernel against the separate torch ops of the comparison
     model: same roundings, so equal except where the row's sum of squares (another summation
     order) moves rstd by an ulp."""
     from blackwell_diffusion_rtx6000_5090_i2v_b200 import dit, nvfp4
-    D = 128
-    cfg = dit.WanDiTConfig(dim=heads * D, heads=heads, ffn=1024, layers=1, in_channels=16, out_channels=16)
+    cfg = dit.WanDiTConfig(dim=heads * D, heads=heads, ffn=1024, layers=1, in_channels=16, out_channels=16,
+                           head_dim=D)
     g = torch.Generator(device="cuda").manual_seed(L + heads)
     qkv = (torch.randn(L, 3 * heads * D, generator=g, device="cuda") * 2).to(torch.bfloat16)
     gq = 1 + 0.1 * torch.randn(heads * D, generator=g, device="cuda")

@@ -56,3 +56,12 @@ def test_static_linear_rejects_oversized_problems():
     rc = N.lib.nvfp4_linear_bf16_static(None, limit // 4096 + 1, 4096, None, None, None, 256,
                                         None, 0, None, None, None)
     assert rc == 1
+    # few elements, but the padded scale layout (rows to 256, K to 256) outgrows its 1 MiB
+    rc = N.lib.nvfp4_linear_bf16_static(None, 1, 131072, None, None, None, 256, None, 0, None,
+                                        None, None)
+    assert rc == 1
+    # extents whose product wraps a 64-bit integer are refused before anything is multiplied
+    for m, k in ((1 << 62, 32), (1 << 40, 1 << 40), (3, (1 << 62) + 32)):
+        rc = N.lib.nvfp4_linear_bf16_static(None, m, k, None, None, None, 256, None, 0, None,
+                                            None, None)
+        assert rc == 1, (m, k)
