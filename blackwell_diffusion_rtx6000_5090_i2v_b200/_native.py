@@ -37,6 +37,8 @@ SIGNATURES = {
     "nvfp4_swizzle_scales": (_i, [_p, _i64, _i64, _p, _p]),
     "nvfp4_gemm": (_i, [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _f, _f, _p, _p, _p, _i, _p,
                         _p, _p, _p]),
+    "nvfp4_gemm_set_tiling": (_i, [_i]),
+    "nvfp4_gemm_stacked": (_i, [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _p, _p, _p, _p]),
     "nvfp4_norm_mod_amax_bf16": (_i, [_p, _i64, _i64, _p, _p, _p, _p, _i, _f, _p, _p, _p, _p, _p]),
     "nvfp4_norm_mod_quantize_bf16": (_i, [_p, _i64, _i64, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p,
                                           _p, _p]),

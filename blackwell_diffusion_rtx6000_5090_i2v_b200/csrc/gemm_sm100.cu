@@ -25,11 +25,21 @@
 // cycles; from converged code a copy costs ~8 and the same stage takes 511,
 // the time of the four MMAs alone.
 //
-// Tensor memory (512 columns): two 256-column accumulators at columns 0 and
-// 192 that overlap in [192,256), scale factors at [448,496).  The epilogue
-// reads the overlapping 64 columns into registers first and then lets the
-// issuer start the next tile in the other accumulator, so the rest of the
-// epilogue runs under the next tile's main loop.
+// Two tilings of N share the kernel body (template parameter kAlt):
+//   uniform     256-wide tiles.  Tensor memory (512 columns): two 256-column
+//               accumulators at columns 0 and 192 that overlap in [192,256), scale factors
+//               at [448,496).  The epilogue reads the overlapping 64 columns into registers
+//               first and then lets the issuer start the next tile in the other accumulator,
+//               so the rest of the epilogue runs under the next tile's main loop; what stays
+//               exposed per tile is that hand-off (about 1300 cycles).
+//   alternating N is cut into 448-column pairs of a 256-wide and a 192-wide tile and every CTA
+//               pair takes wide and narrow tiles in turn: the wide accumulator sits at columns
+//               [0,256), the narrow one at [256,448), scale factors at [448,496) -- no shared
+//               columns, so the issuer goes straight on to the next tile and an accumulator
+//               is handed back only two tiles later.  Costs 7 % more operand bytes per flop;
+//               pays when the main loop is short (K up to a few thousand).  In odd pairs the
+//               narrow tile comes first so that every tile starts 0 or 64 rows into a 128-row
+//               scale atom and two atoms always cover it.
 //
 // Every wait is bounded: when a wait gives up the kernel records where in
 // *status, raises a CTA-wide abort flag, and every role leaves its loop so
@@ -56,7 +66,11 @@ constexpr int kEpiBytes = kEpiWarps * kEpiSlabBytes;  // one slab per epilogue w
 constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*align slack*/ + 256 /*barriers*/;
 constexpr int kThreads = 320;          // producer, issuer, eight epilogue warps
 constexpr int kTmemCols = 512;
-constexpr int kAccCol1 = 192;            // second accumulator's first column
+constexpr int kAccCol1 = 192;            // uniform tiling: second accumulator's first column
+constexpr int kAltPair = 448;            // alternating tiling: a 256-wide plus a 192-wide tile
+constexpr int kAltNarrow = 192;
+constexpr int kAltAccCol1 = 256;         // alternating tiling: the narrow accumulator's first column
+constexpr int kBBytesNarrow = (kAltNarrow / 2) * BK / 2;   // 12288: a CTA's 96 rows of B
 constexpr int kSfCol = 448;              // scale factors of one stage: 16 columns of SFA, 32 of SFB
 constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 2 GHz
 
@@ -266,8 +280,10 @@ __device__ __forceinline__ uint64_t desc_sf(uint32_t saddr) {
 // Instruction descriptor, kind::mxf4nvf4: A and B E2M1 (code 1) both K-major,
 // N at bits 17-22 in units of 8, UE4M3 scales (bit 23 clear), M at bits 24-28
 // in units of 16, scale-factor ids 0, K = 64 (bit 31 clear).
-constexpr uint32_t kIdesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
-                            ((uint32_t)((2 * BM) >> 4) << 24);  // M = 256 across the CTA pair
+__device__ __forceinline__ uint32_t make_idesc(int n) {
+  return (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)((2 * BM) >> 4) << 24);  // M = 256 across the CTA pair
+}
 
 __device__ __forceinline__ float gelu_tanh(float x) {
   // 0.5 x (1 + tanh(u)) = x / (1 + exp(-2u)), u = sqrt(2/pi) (x + 0.044715 x^3): one ex2 and
@@ -326,13 +342,70 @@ struct Params {
   int* status;
   float alpha, beta;
   int M, N, K;
-  int m_tiles, n_tiles, k_tiles, k_atoms;
+  int m_tiles, k_tiles, k_atoms;
+  int n_a, n_b;       // uniform tiling: 256-wide tile columns, 0; alternating: wide, narrow columns
+  int gb_group;       // 0: gb is one scalar; else gb[n / gb_group] (weights of several tensors
+                      // stacked along N, each with its own tensor scale)
   int act;
 };
 
+// One output tile as every role sees it.
+struct Tile {
+  int mt;       // 256-row tile index
+  int n0;       // first column
+  int w;        // columns the MMA computes: 256 (uniform); 64..256 in steps of 64 (alternating)
+  int buf;      // accumulator: uniform 0/1 by turns; alternating 0 = wide, 1 = narrow
+};
+
+// The sequence of tiles of one CTA pair; producer, issuer and epilogue each walk their own copy.
+// Alternating tiling: wide and narrow tiles form two lists numbered like the uniform tiles
+// (tile_coords over the list's columns); pair q takes items q, q + Q, ... of each list, wide
+// on its even turns and narrow on its odd ones, and finishes whichever list is left over.
+template <bool kAlt>
+struct TileWalk {
+  int m_tiles, N, stride, n_a, n_b, i_a, i_b, t;
+  __device__ TileWalk(const Params& p, int pair, int num_pairs)
+      : m_tiles(p.m_tiles), N(p.N), stride(num_pairs), n_a(p.n_a), n_b(p.n_b), i_a(pair),
+        i_b(pair), t(0) {}
+  __device__ __forceinline__ bool next(Tile& o) {
+    if (!kAlt) {
+      if (i_a >= m_tiles * n_a) return false;
+      int nt;
+      tile_coords(i_a, m_tiles, n_a, o.mt, nt);
+      o.n0 = nt * BN;
+      o.w = BN;
+      o.buf = t & 1;
+      i_a += stride;
+      ++t;
+      return true;
+    }
+    const bool a_left = i_a < m_tiles * n_a, b_left = i_b < m_tiles * n_b;
+    if (!a_left && !b_left) return false;
+    const bool wide = a_left && (!(t & 1) || !b_left);
+    int j;   // column slot = index of the 448-column pair
+    if (wide) {
+      tile_coords(i_a, m_tiles, n_a, o.mt, j);
+      o.n0 = kAltPair * j + ((j & 1) ? kAltNarrow : 0);
+      i_a += stride;
+    } else {
+      tile_coords(i_b, m_tiles, n_b, o.mt, j);
+      o.n0 = kAltPair * j + ((j & 1) ? 0 : BN);
+      i_b += stride;
+    }
+    const int full = wide ? BN : kAltNarrow;
+    const int left = (N - o.n0 + 63) & ~63;       // what is left of N, in whole 64-column groups
+    o.w = left < full ? left : full;
+    o.buf = wide ? 0 : 1;
+    ++t;
+    return true;
+  }
+};
+
+template <bool kAlt>
 __global__ void __launch_bounds__(kThreads, 1)
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
                   const __grid_constant__ CUtensorMap map_b,
+                  const __grid_constant__ CUtensorMap map_b_narrow,
                   const __grid_constant__ CUtensorMap map_sfa,
                   const __grid_constant__ CUtensorMap map_sfb,
                   const __grid_constant__ CUtensorMap map_d,
@@ -352,18 +425,20 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
   auto full_bar = [&](int s) { return bar_base + 8u * s; };                      // leader: the stage landed in both CTAs
   auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };         // local: the stage's MMAs are done
   auto acc_full_bar = [&](int b) { return bar_base + 8u * (2 * kStages + b); };  // local
-  const uint32_t acc_empty_bar = bar_base + 8u * (2 * kStages + 2);              // leader
-  auto c_bar = [&](int w) { return bar_base + 8u * (2 * kStages + 3 + w); };     // local: epilogue warp w's residual tile landed
-  // leader: the column groups of accumulator b that do NOT gate the next tile have been read
-  auto acc_rest_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 3 + kEpiWarps + b); };
-  static_assert(8 * (2 * kStages + 3 + kEpiWarps + 2) <= 248, "barriers overrun their area");
+  // leader.  Uniform tiling: slot 0 = the shared columns of the previous tile have been read.
+  // Alternating tiling: slot b = every epilogue warp has finished reading accumulator b.
+  auto acc_empty_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 2 + b); };
+  auto c_bar = [&](int w) { return bar_base + 8u * (2 * kStages + 4 + w); };     // local: epilogue warp w's residual tile landed
+  // leader, uniform tiling: the column groups of accumulator b that do NOT gate the next tile
+  // have been read
+  auto acc_rest_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 4 + kEpiWarps + b); };
+  static_assert(8 * (2 * kStages + 4 + kEpiWarps + 2) <= 248, "barriers overrun their area");
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();      // 0 = leader of the pair
   const int pair = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
-  const int total_tiles = p.m_tiles * p.n_tiles;  // 256 x 256 pair tiles
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -372,7 +447,10 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     }
     mbar_init(acc_full_bar(0), 1);
     mbar_init(acc_full_bar(1), 1);
-    mbar_init(acc_empty_bar, 2 * 4);  // one arrival per warp that drains the shared columns
+    // uniform: one arrival per warp that drains the shared columns; alternating: one per
+    // epilogue warp of either CTA
+    mbar_init(acc_empty_bar(0), kAlt ? 2 * kEpiWarps : 2 * 4);
+    mbar_init(acc_empty_bar(1), kAlt ? 2 * kEpiWarps : 2 * 4);
     for (int w = 0; w < kEpiWarps; ++w) mbar_init(c_bar(w), 1);
     mbar_init(acc_rest_bar(0), 2 * 4);   // one arrival per warp that reads the other two groups
     mbar_init(acc_rest_bar(1), 2 * 4);
@@ -391,6 +469,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
   cluster_sync_all();   // the peer's barriers exist before anything is sent to them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // first tensor-memory column of accumulator b
+  auto acc_col = [&](int b) -> uint32_t { return b ? (kAlt ? kAltAccCol1 : kAccCol1) : 0; };
 
   if (warp == 0) {
     // ------------------------------------------------------- producer ----
@@ -400,13 +480,19 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     int s = 0;
     uint32_t ph = 0;
     bool ok = true;
-    for (int tile = pair; ok && tile < total_tiles; tile += num_pairs) {
-      int mt, nt;
-      tile_coords(tile, p.m_tiles, p.n_tiles, mt, nt);
-      // first scale atom of this CTA's A rows / of the tile's two 128-column halves
-      const int sfa_atom = (2 * mt + (int)rank) * p.k_atoms;
-      const int sfb_atom0 = (2 * nt) * p.k_atoms;
+    TileWalk<kAlt> walk(p, pair, num_pairs);
+    Tile tl;
+    while (ok && walk.next(tl)) {
+      // first scale atom of this CTA's A rows / of the two 128-row atoms that cover the tile's
+      // columns (a tile starts 0 or 64 rows into its first atom)
+      const int sfa_atom = (2 * tl.mt + (int)rank) * p.k_atoms;
+      const int sfb_atom0 = (tl.n0 >> 7) * p.k_atoms;
       const int sfb_atom1 = sfb_atom0 + p.k_atoms;
+      // this CTA's half of the tile's B rows; the narrow tiles use a 96-row box
+      const bool narrow = kAlt && tl.buf == 1;
+      const int b_row = tl.n0 + (int)rank * (tl.w >> 1);
+      const CUtensorMap* mb = narrow ? &map_b_narrow : &map_b;
+      const uint32_t stage_tx = 2u * (uint32_t)(kStageBytes - (narrow ? kBBytes - kBBytesNarrow : 0));
       for (int kt = 0; kt < p.k_tiles; ++kt) {
         ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, 0x100 + s);
         ok = __all_sync(0xffffffffu, ok);
@@ -416,10 +502,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         // leader alone arms (a remote arrive per stage stalls the issuing thread for
         // thousands of cycles).
         const uint32_t lead_full = mapa_u32(full_bar(s), 0);
-        mbar_expect_tx(full_bar(s), 2 * kStageBytes, rank == 0 ? on : 0u);
-        tma_load_2d(&map_a, lead_full, st, kt * (BK / 2), (2 * mt + (int)rank) * BM, keep, on);
-        tma_load_2d(&map_b, lead_full, st + kABytes, kt * (BK / 2), nt * BN + (int)rank * (BN / 2),
-                    keep, on);
+        mbar_expect_tx(full_bar(s), stage_tx, rank == 0 ? on : 0u);
+        tma_load_2d(&map_a, lead_full, st, kt * (BK / 2), (2 * tl.mt + (int)rank) * BM, keep, on);
+        tma_load_2d(mb, lead_full, st + kABytes, kt * (BK / 2), b_row, keep, on);
         tma_load_2d(&map_sfa, lead_full, st + kABytes + kBBytes, 0, sfa_atom + kt * (BK / 64), keep,
                     on);
         tma_load_2d(&map_sfb, lead_full, st + kABytes + kBBytes + kSfaBytes, 0,
@@ -448,11 +533,17 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      int t = 0;
+      int uses0 = 0, uses1 = 0;                         // tiles each accumulator has held
       const uint32_t sfa_t = tmem_base + kSfCol;        // SFA of K-block j at +4j
-      const uint32_t sfb_t = tmem_base + kSfCol + 16;   // SFB of K-block j at +8j (two halves)
-      for (int tile = pair; ok && tile < total_tiles; tile += num_pairs, ++t) {
-        const uint32_t acc = tmem_base + ((t & 1) ? kAccCol1 : 0);
+      const uint32_t sfb_t = tmem_base + kSfCol + 16;   // SFB of K-block j at +8j (two atoms)
+      TileWalk<kAlt> walk(p, pair, num_pairs);
+      Tile tl;
+      while (ok && walk.next(tl)) {
+        const int t = walk.t - 1;                       // ordinal of this tile
+        const uint32_t acc = tmem_base + acc_col(tl.buf);
+        const uint32_t idesc = make_idesc(tl.w);
+        // the tile's first column inside its first scale atom, in 32-row column units
+        const uint32_t sfb_off = (uint32_t)(tl.n0 & 127) >> 5;
         for (int kt = 0; kt < p.k_tiles; ++kt) {
           ok = mbar_wait(full_bar(s), ph, abort_flag, p.status, 0x200 + s);
           ok = __all_sync(0xffffffffu, ok);
@@ -467,23 +558,36 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
             tc_cp_sf_pair(sfb_t + 8 * j, desc_sf(sfb_s + j * kSfAtomBytes), on);
             tc_cp_sf_pair(sfb_t + 8 * j + 4, desc_sf(sfb_s + kSfbBytes / 2 + j * kSfAtomBytes), on);
           }
-          if (kt == 0 && t > 0) {
-            // Only the MMAs need the previous tile's shared accumulator columns drained; the
-            // scale copies above went ahead of this wait (they follow the previous tile's MMAs
-            // in issue order, which is all the single scale buffer needs).
-            ok = mbar_wait(acc_empty_bar, (uint32_t)(t - 1) & 1u, abort_flag, p.status, 0x300);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            if (t >= 2) {
-              // This accumulator was last used two tiles ago.  The warps that own its shared
-              // group have been through it (they arrived above for the tile in between); the
-              // warps that own its other two groups are tracked here.  They are normally a
-              // whole main loop ahead, so this wait costs nothing; without it a short K and a
-              // slow residual load could let these MMAs overwrite columns not yet read.
-              ok = mbar_wait(acc_rest_bar(t & 1), (uint32_t)((t >> 1) - 1) & 1u, abort_flag,
-                             p.status, 0x310);
+          if (kt == 0) {
+            // Only the MMAs need the accumulator; the scale copies above went ahead of these
+            // waits (they follow the previous tile's MMAs in issue order, which is all the
+            // single scale buffer needs).
+            if (kAlt) {
+              // the epilogue of this accumulator's previous tile (two tiles back when wide and
+              // narrow alternate) has read all of it
+              const int used = tl.buf ? uses1 : uses0;
+              if (used > 0) {
+                ok = mbar_wait(acc_empty_bar(tl.buf), (uint32_t)(used - 1) & 1u, abort_flag,
+                               p.status, 0x300 + tl.buf);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+              }
+            } else if (t > 0) {
+              // the previous tile's shared accumulator columns have been drained
+              ok = mbar_wait(acc_empty_bar(0), (uint32_t)(t - 1) & 1u, abort_flag, p.status, 0x300);
               ok = __all_sync(0xffffffffu, ok);
               if (!ok) break;
+              if (t >= 2) {
+                // This accumulator was last used two tiles ago.  The warps that own its shared
+                // group have been through it (they arrived above for the tile in between); the
+                // warps that own its other two groups are tracked here.  They are normally a
+                // whole main loop ahead, so this wait costs nothing; without it a short K and a
+                // slow residual load could let these MMAs overwrite columns not yet read.
+                ok = mbar_wait(acc_rest_bar(t & 1), (uint32_t)((t >> 1) - 1) & 1u, abort_flag,
+                               p.status, 0x310);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+              }
             }
             tc_fence_after();
           }
@@ -492,7 +596,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
           for (int j = 0; j < BK / 64; ++j) {
             // 64 elements = 32 bytes along K inside the swizzled row: +2 in 16-byte units
-            tc_mma_nvf4(acc, da + 2 * j, db + 2 * j, kIdesc, sfa_t + 4 * j, sfb_t + 8 * j,
+            tc_mma_nvf4(acc, da + 2 * j, db + 2 * j, idesc, sfa_t + 4 * j, sfb_t + 8 * j + sfb_off,
                         (kt | j) != 0, on);
           }
           tc_commit_pair(empty_bar(s), 3, on);   // both CTAs' producers may refill the stage
@@ -502,19 +606,23 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
           }
         }
         if (!ok) break;
-        tc_commit_pair(acc_full_bar(t & 1), 3, on);
+        tc_commit_pair(acc_full_bar(tl.buf), 3, on);
+        if (tl.buf) ++uses1; else ++uses0;
       }
     }
   } else {
     // ------------------------------------------------------- epilogue ----
     // Eight warps: warp w reads tensor-memory lanes 32*(w%4).. (rows of this CTA), warps 2-5
-    // take the first two 64-column groups in processing order (the shared one first), warps
-    // 6-9 the other two.  A group goes through the warp's 32 x 128-byte shared-memory slab
-    // (128-byte swizzle, so that the lane-per-row writes spread over the banks) and leaves
-    // with one TMA store, which also clips at M and N.
+    // take the first two 64-column groups in processing order, warps 6-9 the other two (a
+    // narrow tile has three groups or fewer: the warps without one only pass the barriers).
+    // A group goes through the warp's 32 x 128-byte shared-memory slab (128-byte swizzle, so
+    // that the lane-per-row writes spread over the banks) and leaves with one TMA store, which
+    // also clips at M and N.
     const int q = warp & 3;  // tensor-memory lane quarter this warp may read
-    const float scale = p.alpha * (p.ga ? __ldg(p.ga) : 1.0f) * (p.gb ? __ldg(p.gb) : 1.0f);
-    const uint32_t lead_acc_empty = mapa_u32(acc_empty_bar, 0);
+    const float scale_a = p.alpha * (p.ga ? __ldg(p.ga) : 1.0f);
+    const float scale_ab = scale_a * ((p.gb && p.gb_group == 0) ? __ldg(p.gb) : 1.0f);
+    const uint32_t lead_acc_empty0 = mapa_u32(acc_empty_bar(0), 0);
+    const uint32_t lead_acc_empty1 = mapa_u32(acc_empty_bar(1), 0);
     const uint32_t on = elect_one();
     const uint64_t stream_out = l2_policy_evict_first();
     uint32_t amax2 = 0u;                 // running max |D| of this thread, as a bf16 pair
@@ -522,36 +630,47 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     const int g_first = warp >= 6 ? 2 : 0;   // this warp's groups: g_first, g_first + 1
     bool ok = true;
     uint32_t c_phase = 0;                // parity of this warp's residual-tile barrier
-    int t = 0;
-    for (int tile = pair; ok && tile < total_tiles; tile += num_pairs, ++t) {
-      int mt, nt;
-      tile_coords(tile, p.m_tiles, p.n_tiles, mt, nt);
-      const int buf = t & 1;
-      ok = mbar_wait(acc_full_bar(buf), (uint32_t)(t >> 1) & 1u, abort_flag, p.status, 0x400 + buf);
+    int uses0 = 0, uses1 = 0;
+    TileWalk<kAlt> walk(p, pair, num_pairs);
+    Tile tl;
+    while (ok && walk.next(tl)) {
+      const int buf = tl.buf;
+      const uint32_t lead_acc_empty = buf ? lead_acc_empty1 : lead_acc_empty0;
+      ok = mbar_wait(acc_full_bar(buf), (uint32_t)(buf ? uses1 : uses0) & 1u, abort_flag, p.status,
+                     0x400 + buf);
+      if (buf) ++uses1; else ++uses0;
       // the whole warp must agree before the .sync.aligned loads below
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const int row0 = (2 * mt + (int)rank) * BM + q * 32;
+      const int row0 = (2 * tl.mt + (int)rank) * BM + q * 32;
       const int row = row0 + lane;
-      const uint32_t acc = tmem_base + ((uint32_t)(q * 32) << 16) + (buf ? kAccCol1 : 0);
-      constexpr int kGroups = BN / 64;   // 64-column groups; the first one processed is the
-                                         // one both accumulators share
+      const uint32_t acc = tmem_base + ((uint32_t)(q * 32) << 16) + acc_col(buf);
+      constexpr int kGroups = BN / 64;   // uniform tiling: the first group processed is the one
+                                         // both accumulators share
       static_assert(256 - kAccCol1 == 64, "the shared columns must be exactly one group");
+      const int n_groups = tl.w >> 6;
+      // alternating tiling: the last group this warp reads (-1: none)
+      const int last_gi = g_first >= n_groups ? -1 : (g_first + 1 < n_groups ? g_first + 1 : n_groups - 1);
+      if (kAlt && last_gi < 0) {
+        // nothing of this tile is ours; the accumulator's barrier still counts every warp
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(lead_acc_empty);
+        continue;
+      }
       uint32_t x[64];
-      auto load_group = [&](int gi, uint32_t (&dst)[64]) {
-        const int cg = buf ? gi : (gi + kGroups - 1) % kGroups;
-        tc_ld_32x32(acc + cg * 64, *reinterpret_cast<uint32_t(*)[32]>(&dst[0]));
-        tc_ld_32x32(acc + cg * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&dst[32]));
-      };
 #pragma unroll 1
       for (int gj = 0; gj < 2; ++gj) {
         const int gi = g_first + gj;
-        const int cg = buf ? gi : (gi + kGroups - 1) % kGroups;
-        const int col0 = nt * BN + cg * 64;
+        if (kAlt && gi > last_gi) break;
+        // tensor-memory column group: the uniform tiling walks them so that the shared group
+        // comes first
+        const int cg = kAlt ? gi : (buf ? gi : (gi + kGroups - 1) % kGroups);
+        const int col0 = tl.n0 + cg * 64;
         // tensor-memory loads first (they are asynchronous until the wait below): for the
         // shared group they sit on the path to the next tile's first MMA
-        load_group(gi, x);
+        tc_ld_32x32(acc + cg * 64, *reinterpret_cast<uint32_t(*)[32]>(&x[0]));
+        tc_ld_32x32(acc + cg * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&x[32]));
         // The residual tile (32 rows x 64 columns of C) comes into the slab by one TMA load, in
         // the layout the result will leave in, while tensor memory is being read: as per-lane
         // row-strided 16-byte loads it put sixteen exposed global-memory latencies per tile on
@@ -564,11 +683,18 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
           tma_load_2d_local(&map_c, c_bar(warp - 2), smem_u32(slab), col0, row0, stream_out, on);
         }
         tc_wait_ld();
-        if (gi == 0) {
+        if (kAlt) {
+          if (gi == last_gi) {
+            // this warp is done with the accumulator
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(lead_acc_empty);
+          }
+        } else if (gi == 0) {
           // the shared columns are in registers: the issuer may start the next tile
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(lead_acc_empty);
+          if (lane == 0) mbar_arrive_cluster(lead_acc_empty0);
         } else if (gi == kGroups - 1) {
           // the last of the other groups is in registers: this accumulator may be reused
           tc_fence_before();
@@ -584,6 +710,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
                         ? __ldg(reinterpret_cast<const uint4*>(p.bias + col0 + g * 8))
                         : make_uint4(0, 0, 0, 0);
         }
+        // stacked weights: the tensor scale of the weight this group's columns belong to
+        const float scale = (p.gb_group > 0 && col0 < p.N)
+                                ? scale_a * __ldg(p.gb + col0 / p.gb_group) : scale_ab;
         if (!p.c) {
           // the previous store must have finished reading the slab
           asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
@@ -743,15 +872,66 @@ static bool make_d_map(CUtensorMap* map, void* base, int64_t M, int64_t N) {
 
 using namespace nvfp4;
 
-extern "C" int nvfp4_gemm(const uint8_t* a_packed, const uint8_t* b_packed,
-                          const uint8_t* a_scales_swizzled, const uint8_t* b_scales_swizzled,
-                          const float* a_global_scale_dev, const float* b_global_scale_dev,
-                          int64_t M, int64_t N, int64_t K, float alpha, float beta,
-                          const void* c_bf16, const void* bias_bf16, const float* gate_f32, int act,
-                          void* d_bf16, float* d_amax_dev, int* status_dev, void* stream) {
+namespace {
+
+// 0 = choose per shape, 1 = uniform 256-wide tiles, 2 = alternating 256/192-wide tiles
+int g_tiling_mode = 0;
+// The alternating tiling removes the per-tile accumulator hand-off and adds 8 % to the bytes an
+// SM takes in per flop (the narrow tiles reuse A less).  Measured on B200 the kernel is bound
+// by that intake, not by the hand-off: alternating is 3 % slower at K = 3072 and 8 % slower at
+// K = 14336 than uniform on the Wan 2.2 shapes, so the automatic choice is uniform for every
+// shape and the alternating tiling stays a selectable variant (bit-identical results).
+constexpr int kAltMaxK = 0;
+
+template <bool kAlt>
+int launch_gemm(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_b_narrow,
+                const CUtensorMap& map_sfa, const CUtensorMap& map_sfb, const CUtensorMap& map_d,
+                const CUtensorMap& map_c, const gemm::Params& p, int64_t tiles, cudaStream_t stream) {
+  static bool attr_set[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (cudaFuncSetAttribute(gemm::nvfp4_gemm_kernel<kAlt>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             gemm::kSmemBytes) != cudaSuccess)
+      return NVFP4_ERR_LAUNCH_FAILED;
+    attr_set[dev] = true;
+  }
+  // one CTA pair (cluster of two) per pair of SMs, each pair walking its tiles
+  const int max_pairs = sm_count() / 2;
+  const unsigned pairs = (unsigned)(tiles < max_pairs ? tiles : max_pairs);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  cfg.blockDim = dim3(gemm::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = gemm::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, gemm::nvfp4_gemm_kernel<kAlt>, map_a, map_b, map_b_narrow, map_sfa,
+                         map_sfb, map_d, map_c, p) != cudaSuccess) {
+    cudaGetLastError();
+    return NVFP4_ERR_LAUNCH_FAILED;
+  }
+  return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_ERR_LAUNCH_FAILED;
+}
+
+int gemm_impl(const uint8_t* a_packed, const uint8_t* b_packed, const uint8_t* a_scales_swizzled,
+              const uint8_t* b_scales_swizzled, const float* a_global_scale_dev,
+              const float* b_global_scale_dev, int64_t b_group_rows, int64_t M, int64_t N,
+              int64_t K, float alpha, float beta, const void* c_bf16, const void* bias_bf16,
+              const float* gate_f32, int act, void* d_bf16, float* d_amax_dev, int* status_dev,
+              void* stream) {
   if (M < 0 || N < 0 || K < 0 || N % 8 != 0 || K % 32 != 0) return NVFP4_ERR_BAD_ARG;
   if (act != NVFP4_ACT_NONE && act != NVFP4_ACT_GELU_TANH) return NVFP4_ERR_BAD_ARG;
   if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return NVFP4_ERR_BAD_ARG;
+  // stacked weights: whole 64-column groups per weight, and a scale array to index
+  if (b_group_rows < 0 || b_group_rows % 64 != 0 || (b_group_rows > 0 && !b_global_scale_dev))
+    return NVFP4_ERR_BAD_ARG;
   if (M == 0 || N == 0) return NVFP4_OK;
   if (K == 0) return NVFP4_ERR_BAD_ARG;
   if (!a_packed || !b_packed || !a_scales_swizzled || !b_scales_swizzled || !d_bf16)
@@ -763,9 +943,10 @@ extern "C" int nvfp4_gemm(const uint8_t* a_packed, const uint8_t* b_packed,
   int rc = check_device_sm100();
   if (rc != NVFP4_OK) return rc;
 
-  CUtensorMap map_a, map_b, map_sfa, map_sfb, map_d, map_c;
+  CUtensorMap map_a, map_b, map_b_narrow, map_sfa, map_sfb, map_d, map_c;
   if (!gemm::make_map(&map_a, a_packed, M, K / 2, gemm::BM) ||
       !gemm::make_map(&map_b, b_packed, N, K / 2, gemm::BN / 2) ||
+      !gemm::make_map(&map_b_narrow, b_packed, N, K / 2, gemm::kAltNarrow / 2) ||
       !gemm::make_sf_map(&map_sfa, a_scales_swizzled, sf_row_tiles(M) * sf_k_atoms(K)) ||
       !gemm::make_sf_map(&map_sfb, b_scales_swizzled, sf_row_tiles(N) * sf_k_atoms(K)) ||
       !gemm::make_d_map(&map_d, d_bf16, M, N))
@@ -796,42 +977,66 @@ extern "C" int nvfp4_gemm(const uint8_t* a_packed, const uint8_t* b_packed,
   p.N = (int)N;
   p.K = (int)K;
   p.m_tiles = (int)((M + 2 * gemm::BM - 1) / (2 * gemm::BM));  // 256-row pair tiles
-  p.n_tiles = (int)((N + gemm::BN - 1) / gemm::BN);
   p.k_tiles = (int)((K + gemm::BK - 1) / gemm::BK);
   p.k_atoms = (int)sf_k_atoms(K);
+  p.gb_group = (int)b_group_rows;
   p.act = act;
 
-  static bool attr_set[64];
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(gemm::nvfp4_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             gemm::kSmemBytes) != cudaSuccess)
-      return NVFP4_ERR_LAUNCH_FAILED;
-    attr_set[dev] = true;
+  const bool alt = g_tiling_mode == 2 || (g_tiling_mode == 0 && K <= kAltMaxK && N > gemm::BN);
+  if (alt) {
+    // 448-column pairs of a wide and a narrow tile; in odd pairs the narrow one comes first
+    const int full = (int)(N / gemm::kAltPair), rem = (int)(N % gemm::kAltPair);
+    if ((full & 1) == 0) {
+      p.n_a = full + (rem > 0);
+      p.n_b = full + (rem > gemm::BN);
+    } else {
+      p.n_b = full + (rem > 0);
+      p.n_a = full + (rem > gemm::kAltNarrow);
+    }
+  } else {
+    p.n_a = (int)((N + gemm::BN - 1) / gemm::BN);
+    p.n_b = 0;
   }
-  if (d_amax_dev && cudaMemsetAsync(d_amax_dev, 0, sizeof(float),
-                                    reinterpret_cast<cudaStream_t>(stream)) != cudaSuccess)
+
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (d_amax_dev && cudaMemsetAsync(d_amax_dev, 0, sizeof(float), st) != cudaSuccess)
     return NVFP4_ERR_LAUNCH_FAILED;
-  // one CTA pair (cluster of two) per pair of SMs, each pair walking 256x256 tiles
-  const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles;
-  const int max_pairs = sm_count() / 2;
-  const unsigned pairs = (unsigned)(tiles < max_pairs ? tiles : max_pairs);
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(2 * pairs, 1, 1);
-  cfg.blockDim = dim3(gemm::kThreads, 1, 1);
-  cfg.dynamicSmemBytes = gemm::kSmemBytes;
-  cfg.stream = reinterpret_cast<cudaStream_t>(stream);
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, gemm::nvfp4_gemm_kernel, map_a, map_b, map_sfa, map_sfb, map_d, map_c, p) != cudaSuccess) {
-    cudaGetLastError();
-    return NVFP4_ERR_LAUNCH_FAILED;
-  }
-  return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_ERR_LAUNCH_FAILED;
+  const int64_t tiles = (int64_t)p.m_tiles * (p.n_a > p.n_b ? p.n_a : p.n_b);
+  return alt ? launch_gemm<true>(map_a, map_b, map_b_narrow, map_sfa, map_sfb, map_d, map_c, p,
+                                 tiles, st)
+             : launch_gemm<false>(map_a, map_b, map_b_narrow, map_sfa, map_sfb, map_d, map_c, p,
+                                  tiles, st);
+}
+
+}  // namespace
+
+extern "C" int nvfp4_gemm_set_tiling(int mode) {
+  if (mode < 0 || mode > 2) return NVFP4_ERR_BAD_ARG;
+  g_tiling_mode = mode;
+  return NVFP4_OK;
+}
+
+extern "C" int nvfp4_gemm(const uint8_t* a_packed, const uint8_t* b_packed,
+                          const uint8_t* a_scales_swizzled, const uint8_t* b_scales_swizzled,
+                          const float* a_global_scale_dev, const float* b_global_scale_dev,
+                          int64_t M, int64_t N, int64_t K, float alpha, float beta,
+                          const void* c_bf16, const void* bias_bf16, const float* gate_f32, int act,
+                          void* d_bf16, float* d_amax_dev, int* status_dev, void* stream) {
+  return gemm_impl(a_packed, b_packed, a_scales_swizzled, b_scales_swizzled, a_global_scale_dev,
+                   b_global_scale_dev, 0, M, N, K, alpha, beta, c_bf16, bias_bf16, gate_f32, act,
+                   d_bf16, d_amax_dev, status_dev, stream);
+}
+
+extern "C" int nvfp4_gemm_stacked(const uint8_t* a_packed, const uint8_t* b_packed,
+                                  const uint8_t* a_scales_swizzled,
+                                  const uint8_t* b_scales_swizzled,
+                                  const float* a_global_scale_dev,
+                                  const float* b_global_scales_dev, int64_t b_rows_per_weight,
+                                  int64_t M, int64_t N, int64_t K, const void* bias_bf16,
+                                  void* d_bf16, int* status_dev, void* stream) {
+  if (b_rows_per_weight <= 0 || b_rows_per_weight % 256 != 0 || N % b_rows_per_weight != 0)
+    return NVFP4_ERR_BAD_ARG;
+  return gemm_impl(a_packed, b_packed, a_scales_swizzled, b_scales_swizzled, a_global_scale_dev,
+                   b_global_scales_dev, b_rows_per_weight, M, N, K, 1.0f, 0.0f, nullptr, bias_bf16,
+                   nullptr, NVFP4_ACT_NONE, d_bf16, nullptr, status_dev, stream);
 }

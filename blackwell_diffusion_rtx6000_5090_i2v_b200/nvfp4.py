@@ -340,6 +340,52 @@ def fp4_gemm(A: FP4Tensor, B: FP4Tensor, alpha: float = 1.0, beta: float = 0.0, 
     return _gemm_packed(A, B, alpha, beta, C, bias, gate, gelu, out, out_amax)
 
 
+class StackedWeights:
+    """Several packed ``[rows, K]`` weights stacked along N so that one GEMM launch serves them
+    all, each keeping its own FP32 tensor scale (additive; ``nvfp4_gemm_stacked``).  Used for
+    the text K/V projections of all DiT blocks, computed once per step before the block loop
+    as the reference's TE model does (fx/src/s4/models/wan22/wan_transformer_megaupload.py:
+    379-382,411-426).  ``rows`` must be a multiple of 256.  The given tensors are re-pointed
+    at their slices of the stacked buffers, so the weights are not held twice."""
+
+    def __init__(self, weights: Sequence[FP4Tensor], biases: Optional[Sequence[torch.Tensor]] = None):
+        first = weights[0]
+        rows, k = first.shape()
+        if rows % 256 != 0:
+            raise RuntimeError("[s4] [nvfp4] [gemm] stacked weights need rows % 256 == 0")
+        for w in weights:
+            if w.shape() != [rows, k] or w._device != first._device:
+                raise RuntimeError("[s4] [nvfp4] [gemm] stacked weights must share shape and device")
+        self.rows, self.k, self.count, self.device = rows, k, len(weights), first._device
+        self.data = torch.cat([w._data for w in weights])
+        self.scales_swz = torch.cat([w.scale_factors_swizzled() for w in weights])
+        self.gscales = torch.cat([w._gscale for w in weights])
+        self.bias = torch.cat([b.reshape(-1) for b in biases]).contiguous() if biases is not None else None
+        nd, ns = first._data.numel(), first._scales_swz.numel()
+        for i, w in enumerate(weights):
+            w._data = self.data[i * nd:(i + 1) * nd]
+            w._scales_swz = self.scales_swz[i * ns:(i + 1) * ns]
+            w._gscale = self.gscales[i:i + 1]
+
+    def gemm(self, a: FP4Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``[M, K]`` packed activation -> bf16 ``[M, rows * count]``; columns
+        ``[i*rows, (i+1)*rows)`` are ``a @ weight_i.T + bias_i``."""
+        m, k = a.shape()
+        if k != self.k or a._device != self.device:
+            raise RuntimeError("[s4] [nvfp4] [gemm] Inner dimensions must match")
+        n = self.rows * self.count
+        if out is None:
+            out = torch.empty((m, n), dtype=torch.bfloat16, device=self.device)
+        with torch.cuda.device(self.device):
+            rc = N.lib.nvfp4_gemm_stacked(N.ptr(a._data), N.ptr(self.data),
+                                          N.ptr(a.scale_factors_swizzled()), N.ptr(self.scales_swz),
+                                          N.ptr(a._gscale), N.ptr(self.gscales), self.rows, m, n, k,
+                                          N.ptr(self.bias), N.ptr(out),
+                                          N.ptr(N.status_word(self.device)), N.stream_ptr())
+        N.check(rc, "[gemm] stacked launch")
+        return out
+
+
 def gemm_fp4_quantized(A: torch.Tensor, B: torch.Tensor, alpha: float = 1.0, beta: float = 0.0,
                        mode: QuantizationMode = QuantizationMode.block_1d, **kw) -> torch.Tensor:
     """Quantize both bf16 operands, then ``fp4_gemm`` (tensor.h:145-154)."""
@@ -388,6 +434,18 @@ def benchmark(A: torch.Tensor, B: torch.Tensor, iterations: int = 100):
     M, K = A.shape
     tflops = 2.0 * M * B.shape[0] * K / avg_ms / 1e9
     return avg_ms, tflops
+
+
+_TILINGS = {"auto": 0, "uniform": 1, "alternating": 2}
+
+
+def set_gemm_tiling(mode: str = "auto") -> None:
+    """How the GEMM cuts N (additive; a tuning and test knob): ``"uniform"`` 256-wide tiles,
+    ``"alternating"`` 256/192-wide tiles on two disjoint accumulators, ``"auto"`` (default) by
+    shape.  The results are bit-identical either way."""
+    if mode not in _TILINGS:
+        raise RuntimeError(f"[s4] [nvfp4] [gemm] unknown tiling {mode!r}")
+    N.check(N.lib.nvfp4_gemm_set_tiling(_TILINGS[mode]), "[gemm] tiling")
 
 
 def check_status() -> None:

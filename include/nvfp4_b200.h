@@ -120,6 +120,32 @@ NVFP4_API int nvfp4_gemm(const uint8_t* a_packed, const uint8_t* b_packed, const
                float beta, const void* c_bf16, const void* bias_bf16, const float* gate_f32,
                int act, void* d_bf16, float* d_amax_dev, int* status_dev, void* stream);
 
+/* Which N tiling nvfp4_gemm uses: 0 = chosen per shape (the default; today always uniform),
+ * 1 = uniform 256-wide tiles, 2 = 448-column pairs of a 256-wide and a 192-wide tile (two
+ * disjoint accumulators in tensor memory: no hand-off between consecutive tiles, 8 % more
+ * operand bytes per flop; measured 3-8 % slower than uniform on B200, kept selectable).
+ * Process-wide; results do not depend on it: every output element is the same sum over K
+ * either way.  A tuning and test knob with no counterpart in
+ * the reference, whose CUTLASS instantiation fixes one 128x128x128 tile
+ * (fx/src/s4/nvfp4/kernel.cu:61-82). */
+NVFP4_API int nvfp4_gemm_set_tiling(int mode);
+
+/* One GEMM against several weights stacked along N: B is [N, K/2] packed with N a multiple of
+ * b_rows_per_weight (itself a multiple of 256), weight i occupying rows [i*b_rows_per_weight,
+ * (i+1)*b_rows_per_weight) with its own FP32 tensor scale b_global_scales_dev[i]; swizzled
+ * scales and bias stacked the same way.  D[M, N] = ga * gb[n / b_rows_per_weight] * sum + bias.
+ * Every output element equals what nvfp4_gemm gives for that weight alone.  Used to compute the
+ * cross-attention K/V projections of the text context for all DiT blocks in one launch before
+ * the block loop (the context does not change from block to block; the reference's TE model
+ * hoists this projection likewise, fx/src/s4/models/wan22/wan_transformer_megaupload.py:379-382,
+ * 411-426) instead of one launch-bound M = 512 GEMM per block. */
+NVFP4_API int nvfp4_gemm_stacked(const uint8_t* a_packed, const uint8_t* b_packed,
+                                 const uint8_t* a_scales_swizzled, const uint8_t* b_scales_swizzled,
+                                 const float* a_global_scale_dev, const float* b_global_scales_dev,
+                                 int64_t b_rows_per_weight, int64_t M, int64_t N, int64_t K,
+                                 const void* bias_bf16, void* d_bf16, int* status_dev,
+                                 void* stream);
+
 /* LayerNorm (rms = 0) or RMSNorm (rms = 1) over each row of x [rows, cols] in fp32, optional
  * affine weight/bias [cols] and adaLN modulation (1 + scale[cols]) * y + shift[cols] (all fp32,
  * all nullable), result rounded to bf16 -- the producer chain in front of the DiT block's QKV,

@@ -14,10 +14,13 @@ TOL = 1e-2
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "nvfp4_cases.npz")
 
 
-@pytest.fixture(scope="module")
-def nv():
+@pytest.fixture(scope="module", params=["uniform", "alternating"])
+def nv(request):
+    """Every test of this file runs under both N tilings of the GEMM."""
     from blackwell_diffusion_rtx6000_5090_i2v_b200 import nvfp4
-    return nvfp4
+    nvfp4.set_gemm_tiling(request.param)
+    yield nvfp4
+    nvfp4.set_gemm_tiling("auto")
 
 
 def _oracle_gemm(oracle, x, w, bias=None, act=0, gate=None, residual=None):
@@ -307,3 +310,55 @@ def test_short_k_many_tiles_repeatable(nv, oracle):
     for i in range(100):
         assert torch.equal(nv.fp4_gemm(a, b, 1.0, 1.0, C=rc, gelu=True), ref), i
     nv.check_status()
+
+
+@pytest.mark.parametrize("M,N,K", [(300, 3072, 512), (1100, 9216, 256), (513, 5120, 1024),
+                                   (256, 448, 128), (257, 520, 96), (4095, 1536, 3072)])
+def test_tilings_agree_bit_for_bit(M, N, K):
+    """Uniform and alternating tilings compute every output element as the same sum over K, so
+    their results are identical bits -- including ragged edges, the narrow tiles that start 64
+    rows into a scale atom, and the fused epilogue."""
+    from blackwell_diffusion_rtx6000_5090_i2v_b200 import nvfp4
+    a = nvfp4.FP4Tensor.from_bfloat16(student_t_bf16((M, K), 7 + M, device="cuda"), linear_scales=False)
+    b = nvfp4.FP4Tensor.from_bfloat16(outlier_weight_bf16((N, K), 8 + N, device="cuda"), linear_scales=False)
+    bias = randn_bf16((N,), 9, 0.01, device="cuda")
+    gate = torch.randn(N, generator=torch.Generator().manual_seed(10)).cuda()
+    res = randn_bf16((M, N), 11, device="cuda")
+    outs = {}
+    try:
+        for mode in ("uniform", "alternating", "auto"):
+            nvfp4.set_gemm_tiling(mode)
+            amax = torch.zeros(1, device="cuda")
+            outs[mode] = (nvfp4.fp4_gemm(a, b), nvfp4.fp4_gemm(a, b, 1.0, 1.0, bias=bias, gate=gate, C=res),
+                          nvfp4.fp4_gemm(a, b, bias=bias, gelu=True, out_amax=amax), amax)
+            nvfp4.check_status()
+    finally:
+        nvfp4.set_gemm_tiling("auto")
+    for mode in ("alternating", "auto"):
+        for got, want in zip(outs[mode], outs["uniform"]):
+            assert torch.equal(got, want), mode
+
+
+def test_stacked_weights_equal_separate_gemms():
+    """Several weights stacked along N, each with its own tensor scale, in one launch: every
+    slice equals the GEMM against that weight alone (the hoisted text K/V projections)."""
+    from blackwell_diffusion_rtx6000_5090_i2v_b200 import nvfp4
+    from blackwell_diffusion_rtx6000_5090_i2v_b200.nvfp4 import StackedWeights
+    M, K, rows, count = 512, 1024, 768, 5
+    x = randn_bf16((M, K), 21, device="cuda")
+    ws = [randn_bf16((rows, K), 30 + i, 0.02 * (1 + i), device="cuda") for i in range(count)]
+    bs = [randn_bf16((rows,), 40 + i, 0.01, device="cuda") for i in range(count)]
+    packed = [nvfp4.FP4Tensor.from_bfloat16(w, linear_scales=False) for w in ws]
+    a = nvfp4.FP4Tensor.from_bfloat16(x, linear_scales=False)
+    stack = StackedWeights(packed, bs)
+    try:
+        for mode in ("uniform", "alternating"):
+            nvfp4.set_gemm_tiling(mode)
+            y = stack.gemm(a)
+            nvfp4.check_status()
+            assert y.shape == (M, rows * count)
+            for i in range(count):
+                want = nvfp4.fp4_gemm(a, packed[i], bias=bs[i])
+                assert torch.equal(y[:, i * rows:(i + 1) * rows], want), (mode, i)
+    finally:
+        nvfp4.set_gemm_tiling("auto")
