@@ -9,30 +9,13 @@ All buffers are allocated up front, so a step launches kernels only.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
 from typing import Dict, List, Optional, Tuple
 
 import torch
 
 from . import _native as N
 from .nvfp4 import FP4Tensor
-
-
-@dataclass(frozen=True)
-class LinearSpec:
-    name: str
-    n: int      # out features
-    k: int      # in features
-    gelu: bool = False
-
-
-def wan_block_specs(dim: int, ffn: int) -> List[LinearSpec]:
-    return [LinearSpec("qkv", 3 * dim, dim), LinearSpec("attn_out", dim, dim),
-            LinearSpec("ffn_up", ffn, dim, gelu=True), LinearSpec("ffn_down", dim, ffn)]
-
-
-WAN22_TI2V_5B = dict(dim=3072, ffn=14336, tokens=27280)   # 1280x704, 121 frames
-WAN22_A14B = dict(dim=5120, ffn=13824, tokens=32760)      # 832x480, 81 frames
+from .shapes import WAN22_A14B, WAN22_TI2V_5B, LinearSpec, wan_block_specs  # noqa: F401  (re-exported)
 
 
 class _QuantScratch:

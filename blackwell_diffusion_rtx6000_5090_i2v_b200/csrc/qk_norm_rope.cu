@@ -16,9 +16,13 @@
 // walks over groups of kR tokens that bulk copies stage in a ring of shared-memory slots, one
 // CTA-wide reduction per group.
 // blockIdx.y selects the tensor: 0 = q, 1 = k, 2 = v (copy only).
+#include "exchange_sync.cuh"
 #include "nvfp4_common.cuh"
 
 namespace nvfp4 {
+
+int exchange_fill_peers(xsync::Peers& peers, void* const* sync_blocks, int world, int rank);  // exchange.cu
+
 namespace {
 
 constexpr int kMaxThreads = 512;
@@ -50,6 +54,8 @@ struct RopeArgs {
   uint8_t* peer[8];            // that buffer on every rank (this rank's own included)
   int heads_per_rank;          // 0: plain form
   int64_t row_offset;          // this rank's first token in the global order
+  int signal;                  // exchange form: raise the peers' flags once the whole grid is done
+  xsync::Peers peers;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -302,6 +308,9 @@ qk_norm_rope_kernel(const RopeArgs p) {
     while (clock64() - t0 < 2000000LL) {
     }
   }
+  // exchange form: the CTA that finishes last tells every rank that this rank's pieces are in
+  // place (flags of kind 0)
+  if (p.signal) xsync::signal_when_grid_done(p.peers, 0, gridDim.x * gridDim.y, false);
 }
 
 int launch_rope(RopeArgs& a, int tensors, cudaStream_t st) {
@@ -387,7 +396,7 @@ extern "C" NVFP4_API int nvfp4_qk_norm_rope_exchange_bf16(
     const void* q_in, const void* k_in, const void* v_in, int64_t in_row_stride, int64_t rows,
     int heads, int head_dim, const float* gain_q, const float* gain_k, float eps,
     const float* cos_sin, void* const* rank_buffers, int world, int64_t row_offset,
-    int* status_dev, void* stream) {
+    void* const* sync_blocks, int rank, int* status_dev, void* stream) {
   const int64_t dim = (int64_t)heads * head_dim;
   if (rows < 0 || heads <= 0 || head_dim <= 0 || head_dim % 16 != 0 || dim > 8 * kC * kMaxThreads ||
       in_row_stride < dim || in_row_stride % 8 != 0 || world < 1 || world > 8 ||
@@ -401,10 +410,17 @@ extern "C" NVFP4_API int nvfp4_qk_norm_rope_exchange_bf16(
     if (!rank_buffers[r]) return NVFP4_ERR_BAD_ARG;
     if (!aligned16(rank_buffers[r])) return NVFP4_ERR_BAD_ALIGN;
   }
+  RopeArgs a{};
+  if (sync_blocks) {
+    // a rank with nothing to send would raise no flag and leave its peers waiting
+    if (rows == 0) return NVFP4_ERR_BAD_ARG;
+    const int prc = exchange_fill_peers(a.peers, sync_blocks, world, rank);
+    if (prc != NVFP4_OK) return prc;
+    a.signal = 1;
+  }
   int rc = check_device_sm100();
   if (rc != NVFP4_OK) return rc;
   if (rows == 0) return NVFP4_OK;
-  RopeArgs a{};
   a.in[0] = static_cast<const uint8_t*>(q_in);
   a.in[1] = static_cast<const uint8_t*>(k_in);
   a.in[2] = static_cast<const uint8_t*>(v_in);

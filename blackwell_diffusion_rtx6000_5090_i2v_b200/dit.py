@@ -38,7 +38,7 @@ import torch.nn.functional as F
 
 from . import _native as N
 from . import ulysses
-from .nvfp4 import FP4Tensor, fp4_gemm
+from .nvfp4 import FP4Tensor, StackedWeights, fp4_gemm
 
 
 @dataclass(frozen=True)
@@ -98,6 +98,20 @@ def _mark(label: str) -> None:
         TIMELINE.mark(label)
 
 
+# Tensor amax of every activation the NVFP4 path quantizes, by linear name: filled while
+# AMAX_RECORD is a dict, and forced onto the comparison model's quantizers while AMAX_PIN is one
+# (the comparison then shares only the per-tensor FP32 scale with the NVFP4 path; block scales
+# and elements are still derived from its own activations).
+AMAX_RECORD: Optional[Dict[str, torch.Tensor]] = None
+AMAX_PIN: Optional[Dict[str, torch.Tensor]] = None
+
+
+def _record_amax(lin: "PackedLinear", t: FP4Tensor) -> FP4Tensor:
+    if AMAX_RECORD is not None:
+        AMAX_RECORD[lin.name] = t.global_amax().clone()
+    return t
+
+
 _E2M1 = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
 
 
@@ -120,9 +134,9 @@ class PackedLinear:
     """A linear whose weight lives only in packed NVFP4 form (bias in bf16)."""
 
     def __init__(self, n: int, k: int, gen: torch.Generator, device, std: float = 0.02,
-                 bias: bool = True):
+                 bias: bool = True, name: str = ""):
         w = (torch.randn(n, k, generator=gen, device=device) * std).to(torch.bfloat16)
-        self.n, self.k = n, k
+        self.n, self.k, self.name = n, k, name
         self.w = FP4Tensor.from_bfloat16(w, linear_scales=True)
         self.bias = ((torch.randn(n, generator=gen, device=device) * 0.01).to(torch.bfloat16)
                      if bias else None)
@@ -136,7 +150,8 @@ class PackedLinear:
         reverses the K axis of both operands -- the same sum in another order, which serves as
         the control for how much a last-bit change in a GEMM moves the step output."""
         x2 = x.reshape(-1, x.shape[-1]).contiguous()
-        xq = dequant_f32(FP4Tensor.from_bfloat16(x2, linear_scales=True))
+        pinned = AMAX_PIN.get(self.name) if AMAX_PIN is not None else None
+        xq = dequant_f32(FP4Tensor.from_bfloat16(x2, linear_scales=True, amax=pinned))
         wq = dequant_f32(self.w)
         if reorder:
             xq, wq = xq.flip(-1).contiguous(), wq.flip(-1).contiguous()
@@ -268,16 +283,16 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor
 
 
 class WanBlock:
-    def __init__(self, cfg: WanDiTConfig, gen: torch.Generator, device):
+    def __init__(self, cfg: WanDiTConfig, gen: torch.Generator, device, name: str = "block"):
         d = cfg.dim
         self.cfg = cfg
-        self.qkv = PackedLinear(3 * d, d, gen, device)
-        self.attn_out = PackedLinear(d, d, gen, device)
-        self.cross_q = PackedLinear(d, d, gen, device)
-        self.cross_kv = PackedLinear(2 * d, d, gen, device)
-        self.cross_out = PackedLinear(d, d, gen, device)
-        self.ffn_up = PackedLinear(cfg.ffn, d, gen, device)
-        self.ffn_down = PackedLinear(d, cfg.ffn, gen, device)
+        self.qkv = PackedLinear(3 * d, d, gen, device, name=f"{name}.qkv")
+        self.attn_out = PackedLinear(d, d, gen, device, name=f"{name}.attn_out")
+        self.cross_q = PackedLinear(d, d, gen, device, name=f"{name}.cross_q")
+        self.cross_kv = PackedLinear(2 * d, d, gen, device, name=f"{name}.cross_kv")
+        self.cross_out = PackedLinear(d, d, gen, device, name=f"{name}.cross_out")
+        self.ffn_up = PackedLinear(cfg.ffn, d, gen, device, name=f"{name}.ffn_up")
+        self.ffn_down = PackedLinear(d, cfg.ffn, gen, device, name=f"{name}.ffn_down")
         ones = lambda: torch.ones(d, device=device)  # noqa: E731
         self.g_q, self.g_k, self.g_cq, self.g_ck = ones(), ones(), ones(), ones()  # unit RMSNorm gains
         self.norm2_w, self.norm2_b = ones(), torch.zeros(d, device=device)
@@ -286,42 +301,53 @@ class WanBlock:
 
     # ---------------------------------------------------------------- parts --
     def _self_attention_fused(self, qkv, cos_sin, group, px=None):
-        """nvfp4 path: one kernel between the QKV linear and attention (or the exchange)."""
+        """nvfp4 path: one kernel between the QKV linear and attention (or the exchange).
+        Returns ``(o [L, dim], amax of o or None)``."""
         cfg = self.cfg
         L = qkv.shape[0]
+        dim = cfg.dim
+        base = qkv.data_ptr()
         if px is not None:
-            # exchange by stores into peer memory, fused into the norm + RoPE kernel
-            dim = cfg.dim
-            base = qkv.data_ptr()
+            # exchange by stores into peer memory, fused into the norm + RoPE kernel; its last
+            # CTA raises the flags the wait below polls
             N.check(N.lib.nvfp4_qk_norm_rope_exchange_bf16(
                 base, base + 2 * dim, base + 4 * dim, 3 * dim, L, cfg.heads, cfg.head_dim,
                 N.ptr(self.g_q), N.ptr(self.g_k), float(cfg.eps), N.ptr(cos_sin),
-                px.qkv_ptrs[px.turn], px.P, px.rank * px.Lp, N.ptr(N.status_word(qkv.device)),
-                N.stream_ptr()), "qk_norm_rope_exchange")
+                px.qkv_ptrs[px.turn], px.P, px.rank * px.Lp, px.sync_ptrs, px.rank,
+                N.ptr(N.status_word(qkv.device)), N.stream_ptr()), "qk_norm_rope_exchange")
             _mark("qk_norm_rope")
-            px.barrier()
+            px.wait(0)
             q, k, v = px.qkv[px.turn].split(cfg.head_dim, dim=-1)
             _mark("exchange")
             o = attention(q, k, v)
             _mark("self_attention")
-            o = px.scatter_attention_output(o)
+            o, amax = px.return_attention_output(o)
             _mark("exchange")
-            return o.reshape(L, cfg.dim)
+            return o.reshape(L, cfg.dim), amax
         if group is None:
             q, k, v = qk_norm_rope(qkv, cfg.heads, cfg.head_dim, self.g_q, self.g_k, cfg.eps, cos_sin)
             _mark("qk_norm_rope")
         else:
-            packed = qk_norm_rope(qkv, cfg.heads, cfg.head_dim, self.g_q, self.g_k, cfg.eps, cos_sin,
-                                  packed=True)
+            # the kernel writes its pieces grouped by destination rank, [P, L/P, H/P, 3D]: the
+            # all-to-all's send buffer, with no packing copy in between
+            import ctypes
+            P = dist.get_world_size(group)
+            Hp = cfg.heads // P
+            send = torch.empty(P, L, Hp, 3 * cfg.head_dim, dtype=torch.bfloat16, device=qkv.device)
+            ptrs = (ctypes.c_void_p * P)(*[send[r].data_ptr() for r in range(P)])
+            N.check(N.lib.nvfp4_qk_norm_rope_exchange_bf16(
+                base, base + 2 * dim, base + 4 * dim, 3 * dim, L, cfg.heads, cfg.head_dim,
+                N.ptr(self.g_q), N.ptr(self.g_k), float(cfg.eps), N.ptr(cos_sin), ptrs, P, 0, None, 0,
+                N.ptr(N.status_word(qkv.device)), N.stream_ptr()), "qk_norm_rope (send layout)")
             _mark("qk_norm_rope")
-            q, k, v = ulysses.seq_to_heads(packed, group).split(cfg.head_dim, dim=-1)
+            q, k, v = ulysses.all_to_all_packed(send, group).split(cfg.head_dim, dim=-1)
             _mark("exchange")
         o = attention(q, k, v)
         _mark("self_attention")
         if group is not None:
             o = ulysses.heads_to_seq(o.contiguous(), group)
             _mark("exchange")
-        return o.reshape(L, cfg.dim)
+        return o.reshape(L, cfg.dim), None
 
     def _self_attention(self, q, k, v, cos, sin, group):
         cfg = self.cfg
@@ -344,17 +370,29 @@ class WanBlock:
 
     def _cross_kv(self, ctx: torch.Tensor, mode: str):
         cfg = self.cfg
-        kv = (self.cross_kv.nvfp4(FP4Tensor.from_bfloat16(ctx, linear_scales=False))
+        kv = (self.cross_kv.nvfp4(_record_amax(self.cross_kv,
+                                               FP4Tensor.from_bfloat16(ctx, linear_scales=False)))
               if mode == "nvfp4" else self.cross_kv.dequant(ctx, reorder=mode == "dequant_reordered"))
+        return self._split_text_kv(kv)
+
+    def _split_text_kv(self, kv: torch.Tensor):
+        """``[C, 2*dim]`` projection of the text context -> normalised k and v, ``[C, heads, D]``."""
+        cfg = self.cfg
         k, v = kv.chunk(2, dim=-1)
-        C = ctx.shape[0]
+        C = kv.shape[0]
         return (rms_norm(k, self.g_ck, cfg.eps).view(C, cfg.heads, cfg.head_dim),
                 v.reshape(C, cfg.heads, cfg.head_dim))
 
     # -------------------------------------------------------------- forward --
     def forward(self, x: torch.Tensor, ctx: torch.Tensor, temb6: torch.Tensor, cos, sin,
                 mode: str = "nvfp4", group=None, cos_sin: Optional[torch.Tensor] = None,
-                px: Optional[ulysses.PeerExchange] = None) -> torch.Tensor:
+                px: Optional[ulysses.PeerExchange] = None, text_kv=None,
+                amax_hook=None) -> torch.Tensor:
+        """``text_kv``: this block's cross-attention ``(k, v)`` when the step computed them
+        for all blocks ahead of the loop.  ``amax_hook(t)``: called on every activation's
+        one-element amax tensor between the amax pass and the packing pass (sharded runs use it
+        to all-reduce the maximum, which makes every shard quantize with the full tensor's
+        scale)."""
         cfg = self.cfg
         mod = self.scale_shift_table + temb6.float()
         shift_msa, scale_msa, gate_msa, c_shift, c_scale, c_gate = (m.contiguous() for m in mod)
@@ -363,34 +401,48 @@ class WanBlock:
             if cos_sin is None:
                 cos_sin = pack_rope_table(cos, sin)
             _mark("other")
-            a = FP4Tensor.from_norm_mod(x, scale=scale_msa, shift=shift_msa, eps=cfg.eps)
+            a = _record_amax(self.qkv, FP4Tensor.from_norm_mod(x, scale=scale_msa, shift=shift_msa,
+                                                               eps=cfg.eps, amax_hook=amax_hook))
             _mark("norm_quantize")
             qkv = self.qkv.nvfp4(a)
             _mark("gemm_qkv")
-            o = self._self_attention_fused(qkv, cos_sin, group, px)
-            oq = FP4Tensor.from_bfloat16(o.contiguous(), linear_scales=False)
+            o, o_amax = self._self_attention_fused(qkv, cos_sin, group, px)
+            if o_amax is not None and amax_hook is not None:
+                amax_hook(o_amax)
+            # with the peer exchange the return kernel has already taken max|o|
+            oq = _record_amax(self.attn_out, FP4Tensor.from_bfloat16(
+                o.contiguous(), linear_scales=False, amax=o_amax,
+                amax_hook=None if o_amax is not None else amax_hook))
             _mark("quantize")
             x = self.attn_out.nvfp4(oq, gate=gate_msa, C=x, beta=1.0)
             _mark("gemm_attn_out")
-            a = FP4Tensor.from_norm_mod(x, weight=self.norm2_w, bias=self.norm2_b, eps=cfg.eps)
+            a = _record_amax(self.cross_q, FP4Tensor.from_norm_mod(
+                x, weight=self.norm2_w, bias=self.norm2_b, eps=cfg.eps, amax_hook=amax_hook))
             _mark("norm_quantize")
             q = self.cross_q.nvfp4(a)
             _mark("gemm_cross_q")
             q = rms_norm_fused(q, cfg.heads, cfg.head_dim, self.g_cq, cfg.eps)
             _mark("qk_norm_rope")
-            ck, cv = self._cross_kv(ctx, mode)
-            _mark("text_kv")
+            if text_kv is None:
+                text_kv = self._cross_kv(ctx, mode)
+                _mark("text_kv")
+            ck, cv = text_kv
             o = attention(q, ck, cv).reshape(L, cfg.dim)
             _mark("cross_attention")
-            oq = FP4Tensor.from_bfloat16(o.contiguous(), linear_scales=False)
+            oq = _record_amax(self.cross_out, FP4Tensor.from_bfloat16(o.contiguous(), linear_scales=False,
+                                                                      amax_hook=amax_hook))
             _mark("quantize")
             x = self.cross_out.nvfp4(oq, C=x, beta=1.0)
             _mark("gemm_cross_out")
-            a = FP4Tensor.from_norm_mod(x, scale=c_scale, shift=c_shift, eps=cfg.eps)
+            a = _record_amax(self.ffn_up, FP4Tensor.from_norm_mod(x, scale=c_scale, shift=c_shift,
+                                                                  eps=cfg.eps, amax_hook=amax_hook))
             _mark("norm_quantize")
             hid = self.ffn_up.nvfp4(a, gelu=True, out_amax=self._amax)
             _mark("gemm_ffn_up")
-            hq = FP4Tensor.from_bfloat16(hid, linear_scales=False, amax=self._amax)
+            if amax_hook is not None:
+                amax_hook(self._amax)
+            hq = _record_amax(self.ffn_down, FP4Tensor.from_bfloat16(hid, linear_scales=False,
+                                                                     amax=self._amax))
             _mark("quantize")
             x = self.ffn_down.nvfp4(hq, gate=c_gate, C=x, beta=1.0)
             _mark("gemm_ffn_down")
@@ -423,21 +475,29 @@ class WanDiT:
         self.patch_w = (torch.randn(d, cfg.in_channels, pt, ph, pw, generator=gen, device=self.device)
                         * 0.02).to(torch.bfloat16)
         self.patch_b = torch.zeros(d, dtype=torch.bfloat16, device=self.device)
-        self.time_in = PackedLinear(d, cfg.freq_dim, gen, self.device)
-        self.time_hidden = PackedLinear(d, d, gen, self.device)
-        self.time_proj = PackedLinear(6 * d, d, gen, self.device)
-        self.text_in = PackedLinear(d, cfg.text_dim, gen, self.device)
-        self.text_hidden = PackedLinear(d, d, gen, self.device)
-        self.blocks: List[WanBlock] = [WanBlock(cfg, gen, self.device)
-                                       for _ in range(layers if layers is not None else cfg.layers)]
+        self.time_in = PackedLinear(d, cfg.freq_dim, gen, self.device, name="time_in")
+        self.time_hidden = PackedLinear(d, d, gen, self.device, name="time_hidden")
+        self.time_proj = PackedLinear(6 * d, d, gen, self.device, name="time_proj")
+        self.text_in = PackedLinear(d, cfg.text_dim, gen, self.device, name="text_in")
+        self.text_hidden = PackedLinear(d, d, gen, self.device, name="text_hidden")
+        self.blocks: List[WanBlock] = [WanBlock(cfg, gen, self.device, name=f"blocks.{i}")
+                                       for i in range(layers if layers is not None else cfg.layers)]
+        # The text context is the same for every block, so the cross-attention K/V projections
+        # of ALL blocks (each with its own weight) run as one stacked GEMM ahead of the block
+        # loop, as the reference's TE model hoists them
+        # (fx/src/s4/models/wan22/wan_transformer_megaupload.py:379-382,411-426), instead of
+        # one launch-bound 512-row GEMM inside every block.
+        self.text_kv = (StackedWeights([b.cross_kv.w for b in self.blocks],
+                                       [b.cross_kv.bias for b in self.blocks])
+                        if (2 * d) % 256 == 0 and self.blocks else None)
         self._rope: Dict[Tuple[int, int, int], Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = {}
         self._px: Dict[Tuple[int, int], ulysses.PeerExchange] = {}
         self.out_table = torch.randn(2, d, generator=gen, device=self.device) / d ** 0.5
-        self.proj_out = PackedLinear(cfg.out_channels * pt * ph * pw, d, gen, self.device)
+        self.proj_out = PackedLinear(cfg.out_channels * pt * ph * pw, d, gen, self.device, name="proj_out")
 
     def _lin(self, lin: PackedLinear, x: torch.Tensor, mode: str, **kw) -> torch.Tensor:
         if mode == "nvfp4":
-            return lin.nvfp4(FP4Tensor.from_bfloat16(x.contiguous(), linear_scales=False),
+            return lin.nvfp4(_record_amax(lin, FP4Tensor.from_bfloat16(x.contiguous(), linear_scales=False)),
                              gelu=kw.get("gelu", False))
         return lin.dequant(x, gelu=kw.get("gelu", False), reorder=mode == "dequant_reordered")
 
@@ -466,11 +526,12 @@ class WanDiT:
         temb, temb6, ctx = self._conditions(t, text, mode)
         return x, cos, sin, cos_sin, temb, temb6, ctx, grid
 
-    def _head(self, x: torch.Tensor, temb: torch.Tensor, mode: str) -> torch.Tensor:
+    def _head(self, x: torch.Tensor, temb: torch.Tensor, mode: str, amax_hook=None) -> torch.Tensor:
         cfg = self.cfg
         shift, scale = (m.contiguous() for m in (self.out_table + temb.float()))
         if mode == "nvfp4":
-            return self.proj_out.nvfp4(FP4Tensor.from_norm_mod(x, scale=scale, shift=shift, eps=cfg.eps))
+            return self.proj_out.nvfp4(_record_amax(self.proj_out, FP4Tensor.from_norm_mod(
+                x, scale=scale, shift=shift, eps=cfg.eps, amax_hook=amax_hook)))
         return self.proj_out.dequant((layer_norm(x, cfg.eps) * (1 + scale) + shift).to(x.dtype),
                                      reorder=mode == "dequant_reordered")
 
@@ -481,13 +542,26 @@ class WanDiT:
         y = y.reshape(f, h, w, pt, ph, pw, cfg.out_channels).permute(6, 0, 3, 1, 4, 2, 5)
         return y.reshape(cfg.out_channels, f * pt, h * ph, w * pw)
 
+    def _text_kv_all(self, ctx: torch.Tensor):
+        """Cross-attention ``(k, v)`` of every block from one stacked GEMM over the text context."""
+        two_d = 2 * self.cfg.dim
+        ctx_q = FP4Tensor.from_bfloat16(ctx.contiguous(), linear_scales=False)
+        for blk in self.blocks:
+            _record_amax(blk.cross_kv, ctx_q)
+        kv = self.text_kv.gemm(ctx_q)
+        return [blk._split_text_kv(kv[:, i * two_d:(i + 1) * two_d]) for i, blk in enumerate(self.blocks)]
+
     def forward(self, latent: torch.Tensor, t: float, text: torch.Tensor, mode: str = "nvfp4",
-                group: Optional[dist.ProcessGroup] = None, exchange: str = "nccl") -> torch.Tensor:
+                group: Optional[dist.ProcessGroup] = None, exchange: str = "nccl",
+                amax_sync: bool = False) -> torch.Tensor:
         """latent ``[C, F, H, W]`` bf16, text ``[512, 4096]`` bf16 -> ``[C_out, F, H, W]``.
         With ``group`` each rank processes its contiguous shard of the token sequence and
         returns the full output (gathered) on every rank.  ``exchange``: ``"nccl"`` (two
         all-to-alls per block) or ``"peer"`` (stores into peer memory fused into the q/k norm +
-        RoPE kernel; NVFP4 mode, ranks of one node)."""
+        RoPE kernel and a return kernel after attention, ordered by flags; NVFP4 mode, ranks of
+        one node).  ``amax_sync``: every sharded activation is quantized with the maximum of
+        the shards' amax (a 4-byte all-reduce per quantizer) instead of its own shard's, i.e.
+        with the FP32 tensor scale the unsharded model uses."""
         x, cos, sin, cos_sin, temb, temb6, ctx, grid = self._embed(latent, t, text, mode)
         L = x.shape[0]
         P = dist.get_world_size(group) if group is not None else 1
@@ -503,9 +577,19 @@ class WanDiT:
             if key not in self._px:
                 self._px[key] = ulysses.PeerExchange(L, self.cfg.heads, self.cfg.head_dim, group, self.device)
             px = self._px[key]
-        for blk in self.blocks:
-            x = blk.forward(x, ctx, temb6, cos, sin, mode, group if P > 1 else None, cos_sin, px)
-        y = self._head(x, temb, mode)
+        hook = None
+        if P > 1 and amax_sync and mode == "nvfp4":
+            def hook(amax_t: torch.Tensor) -> None:
+                dist.all_reduce(amax_t, op=dist.ReduceOp.MAX, group=group)
+        kvs = None
+        if mode == "nvfp4" and self.text_kv is not None:
+            _mark("other")
+            kvs = self._text_kv_all(ctx)
+            _mark("text_kv")
+        for i, blk in enumerate(self.blocks):
+            x = blk.forward(x, ctx, temb6, cos, sin, mode, group if P > 1 else None, cos_sin, px,
+                            kvs[i] if kvs is not None else None, hook)
+        y = self._head(x, temb, mode, hook)
         if P > 1:
             parts = [torch.empty_like(y) for _ in range(P)]
             dist.all_gather(parts, y.contiguous(), group=group)
@@ -537,8 +621,10 @@ class WanDiT:
         it also measures how fast FP4 re-quantization amplifies last-bit differences."""
         x, cos, sin, cos_sin, temb, temb6, ctx, grid = self._embed(latent, t, text, "nvfp4")
         out = []
-        for blk in self.blocks:
-            y = blk.forward(x, ctx, temb6, cos, sin, "nvfp4", None, cos_sin)
+        kvs = self._text_kv_all(ctx) if self.text_kv is not None else None
+        for i, blk in enumerate(self.blocks):
+            y = blk.forward(x, ctx, temb6, cos, sin, "nvfp4", None, cos_sin,
+                            text_kv=kvs[i] if kvs is not None else None)
             ref = blk.forward(x, ctx, temb6, cos, sin, "dequant")
             out.append((_cosine(y, ref), _cosine(y.float() - x.float(), ref.float() - x.float())))
             x = y

@@ -42,6 +42,8 @@ def main(argv=None) -> int:
                     help="single GPU: also time the step replayed from a CUDA graph")
     ap.add_argument("--exchange", choices=["nccl", "peer"], default="nccl",
                     help="head/sequence exchange: all-to-alls, or stores into peer memory")
+    ap.add_argument("--amax-sync", action="store_true",
+                    help="sharded runs: quantize every activation with the all-reduced (max) amax")
     args = ap.parse_args(argv)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -71,11 +73,12 @@ def main(argv=None) -> int:
         backends = [SDPBackend.FLASH_ATTENTION if args.sdpa == "flash" else SDPBackend.CUDNN_ATTENTION]
 
     def step(mode="nvfp4", grp=group, exchange=args.exchange):
+        kw = dict(mode=mode, group=grp, exchange=exchange, amax_sync=args.amax_sync and grp is not None)
         if backends is not None:
             from torch.nn.attention import sdpa_kernel
             with sdpa_kernel(backends):
-                return model.forward(latent, 500.0, text, mode=mode, group=grp, exchange=exchange)
-        return model.forward(latent, 500.0, text, mode=mode, group=grp, exchange=exchange)
+                return model.forward(latent, 500.0, text, **kw)
+        return model.forward(latent, 500.0, text, **kw)
 
     def fence():
         if world > 1:
@@ -127,6 +130,21 @@ def main(argv=None) -> int:
             ctl = step(mode="dequant_reordered")
             checks["cosine_dequant_model_vs_itself_reordered_sums"] = _cos(ref, ctl)
             del ctl
+            # The same two comparisons with the comparison model's activation quantizers using
+            # the per-tensor amax the NVFP4 path had for the same tensor (its block scales and
+            # elements still come from its own activations): isolates how much of the
+            # free-running divergence enters through the FP32 tensor scale.
+            dit.AMAX_RECORD = {}
+            y_rec = step()
+            pinned, dit.AMAX_RECORD = dit.AMAX_RECORD, None
+            checks["recorded_step_equals_step"] = bool(torch.equal(y_rec, y))
+            dit.AMAX_PIN = pinned
+            ref_pin = step(mode="dequant")
+            ctl_pin = step(mode="dequant_reordered")
+            dit.AMAX_PIN = None
+            checks["cosine_vs_dequant_model_pinned_amax"] = _cos(y, ref_pin)
+            checks["cosine_pinned_dequant_model_vs_itself_reordered_sums"] = _cos(ref_pin, ctl_pin)
+            del ref_pin, ctl_pin, y_rec
             if world == 1:
                 per_block = model.compare_blocks(latent, 500.0, text)
                 checks["per_block_same_input_cosine_min"] = min(c for c, _ in per_block)
@@ -162,6 +180,7 @@ def main(argv=None) -> int:
                                    f"{tokens} tokens, text 512x{cfg.text_dim}",
                        "tokens_per_rank": tokens // world, "sdpa": args.sdpa,
                        "exchange": args.exchange if world > 1 else None,
+                       "amax_sync": bool(args.amax_sync and world > 1),
                        "parallelism": f"ulysses{world}" if world > 1 else "single"},
             "all_ms": [round(t, 3) for t in times],
             "components_ms_rank0": {k: round(v, 3) for k, v in sorted(parts.items())},

@@ -82,9 +82,11 @@ class FP4Tensor:
     def from_bfloat16(input: torch.Tensor,
                       mode: QuantizationMode = QuantizationMode.block_1d,
                       *, linear_scales: bool = True, swizzled_scales: bool = True,
-                      amax: Optional[torch.Tensor] = None) -> "FP4Tensor":
+                      amax: Optional[torch.Tensor] = None, amax_hook=None) -> "FP4Tensor":
         """``amax`` (additive): a one-element fp32 device tensor already holding max|input|,
-        e.g. from the GEMM that produced ``input``; the amax pass is then skipped."""
+        e.g. from the GEMM that produced ``input``; the amax pass is then skipped.
+        ``amax_hook`` (additive): called with the amax tensor between the amax pass and the
+        packing pass, e.g. to all-reduce the maximum over the shards of a sharded tensor."""
         if input.dtype != torch.bfloat16:
             raise RuntimeError("[s4] [nvfp4] [tensor] Input must be BFloat16")
         if not input.is_cuda:
@@ -127,6 +129,8 @@ class FP4Tensor:
             if amax is None:
                 N.check(N.lib.nvfp4_amax_bf16(N.ptr(x), rows * cols, N.ptr(self._amax), st),
                         "[tensor] amax")
+                if amax_hook is not None:
+                    amax_hook(self._amax)
             N.check(N.lib.nvfp4_quantize_bf16(N.ptr(x), rows, cols, N.ptr(self._amax),
                                               N.ptr(self._data), N.ptr(self._scales),
                                               N.ptr(self._scales_swz), N.ptr(self._gscale), st),
@@ -137,7 +141,7 @@ class FP4Tensor:
     def from_norm_mod(x: torch.Tensor, *, weight: Optional[torch.Tensor] = None,
                       bias: Optional[torch.Tensor] = None, scale: Optional[torch.Tensor] = None,
                       shift: Optional[torch.Tensor] = None, rms: bool = False, eps: float = 1e-6,
-                      linear_scales: bool = False, return_normed: bool = False):
+                      linear_scales: bool = False, return_normed: bool = False, amax_hook=None):
         """Quantize ``bf16(norm(x) * weight + bias) * (1 + scale) + shift`` without ever
         writing that tensor: the fused producer in front of the DiT block's linears
         (fx/src/s4/models/wan22/wan_transformer.py:204-206,210,218-220).  ``x`` is bf16
@@ -184,6 +188,8 @@ class FP4Tensor:
                                                    1 if rms else 0, float(eps), N.ptr(stats),
                                                    N.ptr(self._amax), N.ptr(normed), status, st),
                     "[tensor] norm+amax")
+            if amax_hook is not None:
+                amax_hook(self._amax)
             N.check(N.lib.nvfp4_norm_mod_quantize_bf16(N.ptr(xc), rows, cols, w_, b_, sc_, sh_,
                                                        N.ptr(stats), N.ptr(self._amax),
                                                        N.ptr(self._data), N.ptr(self._scales),

@@ -42,6 +42,16 @@ def seq_to_heads(x: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> 
     return recv.reshape(P * Lp, H // P, D)
 
 
+def all_to_all_packed(send: torch.Tensor, group: dist.ProcessGroup) -> torch.Tensor:
+    """``send[r]`` = this rank's ``[L/P, H/P, C]`` pieces for rank r (already grouped by
+    destination, as ``nvfp4_qk_norm_rope_exchange_bf16`` writes them) -> ``[L, H/P, C]``: all
+    tokens of this rank's heads, tokens in rank order.  One collective, no packing copies."""
+    P, Lp, Hp, C = send.shape
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send, group=group)
+    return recv.reshape(P * Lp, Hp, C)
+
+
 def heads_to_seq(x: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
     """Inverse of :func:`seq_to_heads`: ``[L, H/P, D]`` -> ``[L/P, H, D]``."""
     P = _world(group)
@@ -70,55 +80,75 @@ class PeerExchange:
     """The two exchanges of a block done by stores into peer memory instead of all-to-alls.
 
     Every rank holds, in symmetric memory mapped by all ranks of the node, a packed
-    ``[L, H/P, 3D]`` buffer (its heads of q | k | v for ALL tokens) and an ``[L/P, H, D]`` buffer
-    (all heads of the attention output for ITS tokens).  The q/k norm + RoPE kernel of each rank
-    stores its tokens' pieces straight into the owning ranks' packed buffers over NVLink
-    (``nvfp4_qk_norm_rope_exchange_bf16``), and after attention each rank copies its heads'
-    output rows into the owning ranks' output buffers.  What remains of the collective is one
-    tiny all-reduce after each set of stores, which orders the consumers on every rank after
-    the producers on all ranks.  Two sets of buffers alternate from block to block: a rank can
-    be at most one barrier ahead of a peer, so it never overwrites a buffer a peer still reads.
+    ``[L, H/P, 3D]`` buffer (its heads of q | k | v for ALL tokens), an ``[L/P, H, D]`` buffer
+    (all heads of the attention output for ITS tokens) and a small sync block.  The q/k norm +
+    RoPE kernel of each rank stores its tokens' pieces straight into the owning ranks' packed
+    buffers over NVLink (``nvfp4_qk_norm_rope_exchange_bf16``); after attention one kernel
+    moves each rank's head columns into the owning ranks' output buffers and takes max|o| on
+    the way (``nvfp4_attn_return_exchange_bf16``).  The last CTA of either kernel raises this
+    rank's flag in every rank's sync block, and a one-warp kernel with a bounded wait
+    (``nvfp4_exchange_wait``) holds the consumer's stream until all ranks' flags are up: no
+    collective call is left in the block.  Two sets of buffers alternate from block to block:
+    passing a wait means every peer has passed the previous one, so a rank never overwrites a
+    buffer a peer still reads.
 
     Plain loads and stores only -- no multicast mapping is created or used.
     """
 
     def __init__(self, tokens_total: int, heads: int, head_dim: int, group: dist.ProcessGroup,
-                 device: torch.device):
+                 device: torch.device, wait_limit_s: float = 20.0):
         import ctypes
         import os
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm
+        from . import _native as N
         P, r = dist.get_world_size(group), dist.get_rank(group)
         if heads % P or tokens_total % P:
             raise ValueError("heads and tokens must divide by the world size")
         self.group, self.P, self.rank = group, P, r
         self.L, self.Lp, self.H, self.Hp, self.D = tokens_total, tokens_total // P, heads, heads // P, head_dim
-        self.qkv, self.o, self.qkv_ptrs, self.o_peer = [], [], [], []
+        self.wait_limit_ns = int(wait_limit_s * 1e9)
+        self.qkv, self.o, self.qkv_ptrs, self.o_ptrs = [], [], [], []
+
+        def ptr_array(handle):
+            return (ctypes.c_void_p * P)(*[int(p) for p in handle.buffer_ptrs])
+
         for _ in range(2):
             t = symm.empty((self.L, self.Hp, 3 * head_dim), dtype=torch.bfloat16, device=device)
-            h = symm.rendezvous(t, group)
             self.qkv.append(t)
-            self.qkv_ptrs.append((ctypes.c_void_p * P)(*[int(p) for p in h.buffer_ptrs]))
+            self.qkv_ptrs.append(ptr_array(symm.rendezvous(t, group)))
             t = symm.empty((self.Lp, heads, head_dim), dtype=torch.bfloat16, device=device)
-            h = symm.rendezvous(t, group)
             self.o.append(t)
-            self.o_peer.append([h.get_buffer(s, (self.Lp, heads, head_dim), torch.bfloat16)
-                                for s in range(P)])
-        self._flag = torch.zeros(1, dtype=torch.float32, device=device)
+            self.o_ptrs.append(ptr_array(symm.rendezvous(t, group)))
+        self.sync = symm.empty((N.lib.nvfp4_exchange_sync_bytes() // 4,), dtype=torch.int32, device=device)
+        self.sync.zero_()
+        self.sync_ptrs = ptr_array(symm.rendezvous(self.sync, group))
+        self.amax = torch.zeros(1, dtype=torch.float32, device=device)   # of the assembled attention output
         self.turn = 0
+        # every rank's sync block is zero before any peer can raise a flag in it
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
 
-    def barrier(self) -> None:
-        """Stream-ordered: every rank's work enqueued before it is complete on every rank
-        before anything enqueued after it starts."""
-        dist.all_reduce(self._flag, group=self.group)
+    def wait(self, kind: int, amax_out: Optional[torch.Tensor] = None) -> None:
+        """Hold the current stream until all ranks' producer kernels of this exchange are done
+        (``kind`` 0: q|k|v pieces, 1: attention output)."""
+        from . import _native as N
+        N.check(N.lib.nvfp4_exchange_wait(self.sync.data_ptr(), kind, self.P, self.wait_limit_ns,
+                                          N.ptr(amax_out), N.ptr(N.status_word(self.sync.device)),
+                                          N.stream_ptr()), "exchange wait")
 
-    def scatter_attention_output(self, o: torch.Tensor) -> torch.Tensor:
-        """``o`` is ``[L, H/P, D]`` (my heads, all tokens).  Store each rank's token rows into its
-        output buffer and return mine, ``[L/P, H, D]``, once every rank has done the same."""
-        i, r, Lp, Hp = self.turn, self.rank, self.Lp, self.Hp
-        for s in range(self.P):
-            self.o_peer[i][s][:, r * Hp:(r + 1) * Hp, :].copy_(o[s * Lp:(s + 1) * Lp])
-        self.barrier()
-        out = self.o[i]
+    def return_attention_output(self, o: torch.Tensor):
+        """``o`` is ``[L, H/P, D]`` (my heads, all tokens).  Returns ``([L/P, H, D] buffer holding
+        all heads of my tokens, its amax as a one-element device tensor)`` once every rank's
+        stores have landed."""
+        from . import _native as N
+        if o.shape != (self.L, self.Hp, self.D) or o.dtype != torch.bfloat16 or o.stride(2) != 1:
+            raise RuntimeError("return_attention_output: o must be bf16 [L, H/P, D] with unit inner stride")
+        i = self.turn
+        N.check(N.lib.nvfp4_attn_return_exchange_bf16(o.data_ptr(), o.stride(0), o.stride(1), self.L,
+                                                      self.Hp, self.D, self.o_ptrs[i], self.sync_ptrs,
+                                                      self.P, self.rank, N.stream_ptr()),
+                "attention return exchange")
+        self.wait(1, self.amax)
         self.turn ^= 1
-        return out
+        return self.o[i], self.amax

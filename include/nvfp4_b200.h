@@ -199,15 +199,49 @@ NVFP4_API int nvfp4_qk_norm_rope_bf16(const void* q_in, const void* k_in, const 
  * bf16 [tokens_total, heads/world, 3*head_dim] buffer as mapped in THIS process (its own buffer
  * for r = this rank, peer-mapped memory otherwise).  Each thread stores its q | k | v pieces of
  * this rank's `rows` tokens, global token index row_offset + row, straight into the buffer of
- * the rank that owns the head: plain stores over NVLink, no staging copy, no collective.  The
- * caller orders the consumers after all ranks' kernels (a barrier on the same streams). */
+ * the rank that owns the head: plain stores over NVLink, no staging copy, no collective.
+ * sync_blocks (nullable; a HOST array of `world` device pointers to every rank's sync block of
+ * nvfp4_exchange_sync_bytes() bytes, zeroed once, mapped in this process) makes the CTA that
+ * finishes last raise this rank's flag of kind 0 on every rank; the consumers then order
+ * themselves with nvfp4_exchange_wait.  Without it the caller orders the consumers after all
+ * ranks' kernels itself (a barrier on the same streams). */
 NVFP4_API int nvfp4_qk_norm_rope_exchange_bf16(const void* q_in, const void* k_in, const void* v_in,
                                                int64_t in_row_stride, int64_t rows, int heads,
                                                int head_dim, const float* gain_q,
                                                const float* gain_k, float eps,
                                                const float* cos_sin, void* const* rank_buffers,
-                                               int world, int64_t row_offset, int* status_dev,
-                                               void* stream);
+                                               int world, int64_t row_offset,
+                                               void* const* sync_blocks, int rank,
+                                               int* status_dev, void* stream);
+
+/* Bytes of one rank's sync block (flags, epochs and partial maxima of the exchanges). */
+NVFP4_API int64_t nvfp4_exchange_sync_bytes(void);
+
+/* Wait, on the stream, until every rank's flag of `kind` (0: the q|k|v pieces before attention,
+ * 1: the attention output after it) in THIS rank's sync block has reached this rank's next
+ * epoch, i.e. until all ranks' producer kernels of this exchange have finished storing.  One
+ * tiny kernel that polls with plain loads; limit_ns bounds the wait: when it runs out the
+ * kernel stores 0xB00 + (the first missing rank) in *status_dev (nullable) and returns
+ * normally -- the GPU is never left spinning.  For kind 1, amax_out_dev (nullable) receives the
+ * tensor amax of the assembled attention output (the maximum over the sources' partial maxima),
+ * ready for nvfp4_quantize_bf16.  No reference counterpart. */
+NVFP4_API int nvfp4_exchange_wait(void* sync_block, int kind, int world, int64_t limit_ns,
+                                  float* amax_out_dev, int* status_dev, void* stream);
+
+/* The head -> sequence return exchange after attention, as one kernel of plain stores: o is
+ * this rank's attention output, bf16 [tokens_total, heads_local, head_dim] with the given
+ * token and head strides (in elements); the rows of rank s's tokens go into rank_buffers[s]
+ * (bf16 [tokens_total/world, heads_local*world, head_dim], mapped here) at this rank's head
+ * columns.  The same pass takes max|o| per destination; the last CTA publishes those maxima
+ * and raises this rank's flag of kind 1 on every rank (see nvfp4_exchange_wait).  Replaces the
+ * second all-to-all of the Ulysses exchange and the amax pass of the attention-out linear's
+ * quantizer; the reference's attention call sites are fx/src/s4/models/wan22/
+ * wan_transformer.py:126-129 (no distributed counterpart). */
+NVFP4_API int nvfp4_attn_return_exchange_bf16(const void* o_bf16, int64_t o_row_stride,
+                                              int64_t o_head_stride, int64_t tokens_total,
+                                              int heads_local, int head_dim,
+                                              void* const* rank_buffers, void* const* sync_blocks,
+                                              int world, int rank, void* stream);
 
 /* Has no counterpart in the reference.  One whole linear, y = act(x W^T + bias), for
  * callers that cannot allocate device memory (code inside a region where cudaMalloc is not

@@ -13,7 +13,10 @@
  *   - scale bytes: against the reference's own kernel
  *     block_1d_quantization_kernel_te (fx/src/s4/nvfp4/quantization_te.cu:92)
  *     compiled from the reference tree by oracle/Makefile into oracle/_ref and
- *     run on a B200; its outputs are committed under tests/golden/.
+ *     run on a B200: its scale bytes for the golden cases are committed as
+ *     tests/golden/ref_te_scales.npz (written by tests/golden/make_ref_scales.py)
+ *     and compared with this file's on CPU and with the shipped kernel's on the
+ *     GPU; where oracle/_ref is present the kernel is also run live.
  *   - E4M3 / E2M1 converters: exhaustively against the CUDA toolkit's host
  *     converters (cuda_fp8.h / cuda_fp4.h), which are the types the reference
  *     casts through (quantization_te.cu:51, quantization_te_clean.cu:70-79).
@@ -29,6 +32,22 @@
 #include <stdlib.h>
 #include <string.h>
 #include <float.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+/* Threads the parallel loops below use (the benchmark's CPU-baseline leg sets it to the host's
+ * core count explicitly: launchers such as torchrun export OMP_NUM_THREADS=1).  Returns the
+ * number in effect. */
+int nvfp4_oracle_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+  return omp_get_max_threads();
+#else
+  (void)n;
+  return 1;
+#endif
+}
 
 #define NVFP4_BLOCK 16
 

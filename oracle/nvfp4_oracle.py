@@ -66,10 +66,17 @@ def lib():
         L.nvfp4_oracle_swizzle_scales.argtypes = [p, i64, i64, p]
         L.nvfp4_oracle_matmul_nt.restype = None
         L.nvfp4_oracle_matmul_nt.argtypes = [p, p, p, i64, i64, i64, C.c_int, p, p, p, p]
+        L.nvfp4_oracle_set_threads.restype = C.c_int
+        L.nvfp4_oracle_set_threads.argtypes = [C.c_int]
         L.nvfp4_oracle_linear.restype = C.c_int
         L.nvfp4_oracle_linear.argtypes = [p, p, p, i64, i64, i64, C.c_int, p]
         _LIB = L
     return _LIB
+
+
+def set_threads(n: int) -> int:
+    """OpenMP threads of the oracle's loops; returns the number in effect."""
+    return int(lib().nvfp4_oracle_set_threads(int(n)))
 
 
 def toolkit():

@@ -122,6 +122,20 @@ def test_golden_vectors(oracle):
     assert np.array_equal(y, g["linear.y"])
 
 
+REF_SCALES = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_te_scales.npz")
+
+
+def test_block_scales_equal_the_reference_kernels(oracle):
+    """The E4M3 block scales the reference's own kernel (block_1d_quantization_kernel_te,
+    fx/src/s4/nvfp4/quantization_te.cu:92-135) produced on a B200 for the golden inputs
+    (tests/golden/make_ref_scales.py) are byte for byte the oracle's."""
+    g, r = np.load(GOLDEN), np.load(REF_SCALES)
+    for name in ("normal", "student_t", "weights", "tiny_blocks", "edge"):
+        assert float(r[f"{name}.amax"]) == float(g[f"{name}.amax"])
+        _, scales, _ = oracle.quantize(g[f"{name}.x"], float(r[f"{name}.amax"]))
+        assert np.array_equal(scales, r[f"{name}.scales"]), name
+
+
 def test_golden_edge_codes(oracle):
     # row 4 of the edge case holds the E2M1 tie points; with amax 3.39e38 elsewhere the row's
     # own block scale decides, so check the block in isolation
