@@ -255,6 +255,7 @@ def dit_step_report(world: int, rank: int, local_rank: int, steps: int = 3):
 
     with torch.no_grad():
         step()                                            # warm-up: tables, exchange buffers
+        nvfp4.check_status()                              # a rank that never showed up ends the leg here
         times = timed(step, steps)
         nvfp4.check_status()
         dit.TIMELINE = dit.Timeline()

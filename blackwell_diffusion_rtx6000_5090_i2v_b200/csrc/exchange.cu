@@ -95,7 +95,10 @@ __global__ void exchange_wait_kernel(int* sync, int kind, int world, long long l
   const int lane = threadIdx.x;
   const int epoch = sync[xsync::kWaited + kind] + 1;
   bool ok = true;
-  if (lane < world) {
+  // Once a wait has run out (the status word is set and nobody has cleared it) later waits do
+  // not spin again: a step with a missing rank costs one time limit, not one per exchange.
+  const bool failed_before = status != nullptr && *reinterpret_cast<volatile int*>(status) != 0;
+  if (lane < world && !failed_before) {
     const int* flag = sync + xsync::kFlag + kind * xsync::kMaxRanks + lane;
     if (xsync::ld_acquire_sys(flag) - epoch < 0) {
       unsigned long long t0, t;

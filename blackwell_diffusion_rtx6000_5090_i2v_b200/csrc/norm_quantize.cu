@@ -41,7 +41,10 @@ namespace {
 constexpr int kMaxThreads = 512;
 constexpr int kMaxJ = 2;          // 2 blocks x 16 elements x 512 threads = 16384 columns
 constexpr int kMaxWarps = kMaxThreads / 32;
-constexpr int kStages = 3;
+#ifndef NVFP4_NORM_STAGES
+#define NVFP4_NORM_STAGES 3
+#endif
+constexpr int kStages = NVFP4_NORM_STAGES;
 constexpr long long kWaitCycles = 4000000000LL;   // about two seconds; then give up
 constexpr int kErrCopyTimeout = 0x900;            // status code: a row group never arrived
 
@@ -104,10 +107,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Contiguous global -> this CTA's shared memory, bytes reported to `bar`.  One destination,
 // nothing broadcast.  Addresses 16-byte aligned, size a multiple of 16.
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar,
-                                          bool evict_first) {
-  if (evict_first) {
+                                          int hint) {
+  if (hint != 0) {
     uint64_t policy;
-    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    if (hint == 1) {
+      asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    } else {
+      asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
+    }
     asm volatile(
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
         "[%0], [%1], %2, [%3], %4;"
@@ -246,8 +253,14 @@ norm_mod_kernel(const NormArgs p) {
     const uint32_t bytes = (uint32_t)n * row_bytes;
     const uint32_t bar = smem_u32(&full[slot]);
     mbar_expect_tx(bar, bytes);
+#ifdef NVFP4_NORM_TAIL_MB
+    const int64_t tail_rows = ((int64_t)NVFP4_NORM_TAIL_MB << 20) / row_bytes;
+    const int hint = kQuantize ? 1 : (base >= p.rows - tail_rows ? 2 : 1);
+#else
+    const int hint = kQuantize ? 1 : 0;
+#endif
     bulk_load(smem_u32(ring + (size_t)slot * slot_bytes),
-              reinterpret_cast<const uint8_t*>(p.x) + base * row_bytes, bytes, bar, kQuantize);
+              reinterpret_cast<const uint8_t*>(p.x) + base * row_bytes, bytes, bar, hint);
   };
 
   if (threadIdx.x == 0) {
@@ -486,7 +499,9 @@ void shape_for(int units, int* j, int* threads) {
   while (J < kMaxJ && units > J * kMaxThreads) J *= 2;
   // two blocks per thread whenever the row is long enough for two warps: the per-row
   // bookkeeping is then shared by 32 elements instead of 16 (measured 17-20 % faster)
+#ifndef NVFP4_NORM_FORCE_J1
   if (units % 2 == 0 && units / 2 >= 64) J = 2;
+#endif
   const int per = (units + J - 1) / J;
   *j = J;
   *threads = ((per + 31) / 32) * 32;

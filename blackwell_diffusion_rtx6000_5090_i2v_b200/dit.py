@@ -104,12 +104,41 @@ def _mark(label: str) -> None:
 # and elements are still derived from its own activations).
 AMAX_RECORD: Optional[Dict[str, torch.Tensor]] = None
 AMAX_PIN: Optional[Dict[str, torch.Tensor]] = None
+# The packed activation itself (nibbles, linear scales, amax) of every linear, by name: filled
+# by either evaluation mode while QUANT_RECORD is a dict; while QUANT_PIN is one, the comparison
+# model feeds each linear the recorded packed activation instead of quantizing its own input
+# (everything else -- matmul, epilogue, norms, attention, residual stream -- stays its own).
+QUANT_RECORD: Optional[Dict[str, FP4Tensor]] = None
+QUANT_PIN: Optional[Dict[str, FP4Tensor]] = None
+
+
+def _want_linear_scales() -> bool:
+    return QUANT_RECORD is not None
 
 
 def _record_amax(lin: "PackedLinear", t: FP4Tensor) -> FP4Tensor:
     if AMAX_RECORD is not None:
         AMAX_RECORD[lin.name] = t.global_amax().clone()
+    if QUANT_RECORD is not None:
+        QUANT_RECORD[lin.name] = t.snapshot()
     return t
+
+
+def flip_stats(a: Dict[str, FP4Tensor], b: Dict[str, FP4Tensor]) -> Dict[str, Dict[str, float]]:
+    """Per linear name present in both records: the fraction of element codes and of block
+    scale bytes that differ between the two packed activations, and whether the tensor amax
+    does -- where two trajectories of the step part ways, and through which of the three."""
+    out = {}
+    for name, ta in a.items():
+        tb = b.get(name)
+        if tb is None or ta.shape() != tb.shape():
+            continue
+        da, db = ta.quantized_data(), tb.quantized_data()
+        nib = ((da ^ db) & 0x0F).ne(0).float().mean() + ((da ^ db) & 0xF0).ne(0).float().mean()
+        out[name] = {"nibbles_differ": float(nib) / 2,
+                     "block_scales_differ": float(ta.scale_factors().ne(tb.scale_factors()).float().mean()),
+                     "amax_differs": bool(ta.global_amax().item() != tb.global_amax().item())}
+    return out
 
 
 _E2M1 = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
@@ -150,8 +179,14 @@ class PackedLinear:
         reverses the K axis of both operands -- the same sum in another order, which serves as
         the control for how much a last-bit change in a GEMM moves the step output."""
         x2 = x.reshape(-1, x.shape[-1]).contiguous()
-        pinned = AMAX_PIN.get(self.name) if AMAX_PIN is not None else None
-        xq = dequant_f32(FP4Tensor.from_bfloat16(x2, linear_scales=True, amax=pinned))
+        if QUANT_PIN is not None and self.name in QUANT_PIN:
+            xt = QUANT_PIN[self.name]
+        else:
+            pinned = AMAX_PIN.get(self.name) if AMAX_PIN is not None else None
+            xt = FP4Tensor.from_bfloat16(x2, linear_scales=True, amax=pinned)
+        if QUANT_RECORD is not None:
+            QUANT_RECORD[self.name] = xt.snapshot()
+        xq = dequant_f32(xt)
         wq = dequant_f32(self.w)
         if reorder:
             xq, wq = xq.flip(-1).contiguous(), wq.flip(-1).contiguous()
@@ -370,8 +405,8 @@ class WanBlock:
 
     def _cross_kv(self, ctx: torch.Tensor, mode: str):
         cfg = self.cfg
-        kv = (self.cross_kv.nvfp4(_record_amax(self.cross_kv,
-                                               FP4Tensor.from_bfloat16(ctx, linear_scales=False)))
+        kv = (self.cross_kv.nvfp4(_record_amax(self.cross_kv, FP4Tensor.from_bfloat16(
+            ctx, linear_scales=_want_linear_scales())))
               if mode == "nvfp4" else self.cross_kv.dequant(ctx, reorder=mode == "dequant_reordered"))
         return self._split_text_kv(kv)
 
@@ -401,8 +436,10 @@ class WanBlock:
             if cos_sin is None:
                 cos_sin = pack_rope_table(cos, sin)
             _mark("other")
+            ls = _want_linear_scales()
             a = _record_amax(self.qkv, FP4Tensor.from_norm_mod(x, scale=scale_msa, shift=shift_msa,
-                                                               eps=cfg.eps, amax_hook=amax_hook))
+                                                               eps=cfg.eps, amax_hook=amax_hook,
+                                                               linear_scales=ls))
             _mark("norm_quantize")
             qkv = self.qkv.nvfp4(a)
             _mark("gemm_qkv")
@@ -411,13 +448,14 @@ class WanBlock:
                 amax_hook(o_amax)
             # with the peer exchange the return kernel has already taken max|o|
             oq = _record_amax(self.attn_out, FP4Tensor.from_bfloat16(
-                o.contiguous(), linear_scales=False, amax=o_amax,
+                o.contiguous(), linear_scales=ls, amax=o_amax,
                 amax_hook=None if o_amax is not None else amax_hook))
             _mark("quantize")
             x = self.attn_out.nvfp4(oq, gate=gate_msa, C=x, beta=1.0)
             _mark("gemm_attn_out")
             a = _record_amax(self.cross_q, FP4Tensor.from_norm_mod(
-                x, weight=self.norm2_w, bias=self.norm2_b, eps=cfg.eps, amax_hook=amax_hook))
+                x, weight=self.norm2_w, bias=self.norm2_b, eps=cfg.eps, amax_hook=amax_hook,
+                linear_scales=ls))
             _mark("norm_quantize")
             q = self.cross_q.nvfp4(a)
             _mark("gemm_cross_q")
@@ -429,19 +467,20 @@ class WanBlock:
             ck, cv = text_kv
             o = attention(q, ck, cv).reshape(L, cfg.dim)
             _mark("cross_attention")
-            oq = _record_amax(self.cross_out, FP4Tensor.from_bfloat16(o.contiguous(), linear_scales=False,
+            oq = _record_amax(self.cross_out, FP4Tensor.from_bfloat16(o.contiguous(), linear_scales=ls,
                                                                       amax_hook=amax_hook))
             _mark("quantize")
             x = self.cross_out.nvfp4(oq, C=x, beta=1.0)
             _mark("gemm_cross_out")
             a = _record_amax(self.ffn_up, FP4Tensor.from_norm_mod(x, scale=c_scale, shift=c_shift,
-                                                                  eps=cfg.eps, amax_hook=amax_hook))
+                                                                  eps=cfg.eps, amax_hook=amax_hook,
+                                                                  linear_scales=ls))
             _mark("norm_quantize")
             hid = self.ffn_up.nvfp4(a, gelu=True, out_amax=self._amax)
             _mark("gemm_ffn_up")
             if amax_hook is not None:
                 amax_hook(self._amax)
-            hq = _record_amax(self.ffn_down, FP4Tensor.from_bfloat16(hid, linear_scales=False,
+            hq = _record_amax(self.ffn_down, FP4Tensor.from_bfloat16(hid, linear_scales=ls,
                                                                      amax=self._amax))
             _mark("quantize")
             x = self.ffn_down.nvfp4(hq, gate=c_gate, C=x, beta=1.0)
@@ -497,7 +536,8 @@ class WanDiT:
 
     def _lin(self, lin: PackedLinear, x: torch.Tensor, mode: str, **kw) -> torch.Tensor:
         if mode == "nvfp4":
-            return lin.nvfp4(_record_amax(lin, FP4Tensor.from_bfloat16(x.contiguous(), linear_scales=False)),
+            return lin.nvfp4(_record_amax(lin, FP4Tensor.from_bfloat16(x.contiguous(),
+                                                                       linear_scales=_want_linear_scales())),
                              gelu=kw.get("gelu", False))
         return lin.dequant(x, gelu=kw.get("gelu", False), reorder=mode == "dequant_reordered")
 
@@ -531,7 +571,8 @@ class WanDiT:
         shift, scale = (m.contiguous() for m in (self.out_table + temb.float()))
         if mode == "nvfp4":
             return self.proj_out.nvfp4(_record_amax(self.proj_out, FP4Tensor.from_norm_mod(
-                x, scale=scale, shift=shift, eps=cfg.eps, amax_hook=amax_hook)))
+                x, scale=scale, shift=shift, eps=cfg.eps, amax_hook=amax_hook,
+                linear_scales=_want_linear_scales())))
         return self.proj_out.dequant((layer_norm(x, cfg.eps) * (1 + scale) + shift).to(x.dtype),
                                      reorder=mode == "dequant_reordered")
 
@@ -545,7 +586,7 @@ class WanDiT:
     def _text_kv_all(self, ctx: torch.Tensor):
         """Cross-attention ``(k, v)`` of every block from one stacked GEMM over the text context."""
         two_d = 2 * self.cfg.dim
-        ctx_q = FP4Tensor.from_bfloat16(ctx.contiguous(), linear_scales=False)
+        ctx_q = FP4Tensor.from_bfloat16(ctx.contiguous(), linear_scales=_want_linear_scales())
         for blk in self.blocks:
             _record_amax(blk.cross_kv, ctx_q)
         kv = self.text_kv.gemm(ctx_q)

@@ -145,6 +145,27 @@ def main(argv=None) -> int:
             checks["cosine_vs_dequant_model_pinned_amax"] = _cos(y, ref_pin)
             checks["cosine_pinned_dequant_model_vs_itself_reordered_sums"] = _cos(ref_pin, ctl_pin)
             del ref_pin, ctl_pin, y_rec
+            # The comparison model fed, linear by linear, the packed activation the NVFP4 path
+            # quantized (matmuls, epilogues, norms, attention and the residual stream stay its
+            # own): the step-level statement of "same quantized inputs, independent arithmetic".
+            dit.QUANT_RECORD = {}
+            step()
+            shared, dit.QUANT_RECORD = dit.QUANT_RECORD, None
+            dit.QUANT_PIN = shared
+            ref_shared = step(mode="dequant")
+            dit.QUANT_PIN = None
+            checks["cosine_vs_dequant_model_shared_packed_activations"] = _cos(y, ref_shared)
+            del ref_shared
+            # and where the free-running comparison model parts ways with the NVFP4 path: element
+            # codes, block scales or tensor amax, for the first two blocks and the last
+            dit.QUANT_RECORD = {}
+            step(mode="dequant")
+            free, dit.QUANT_RECORD = dit.QUANT_RECORD, None
+            flips = dit.flip_stats(shared, free)
+            keep = [n for n in flips if n.startswith(("blocks.0.", "blocks.1.", f"blocks.{len(model.blocks) - 1}."))]
+            checks["packed_activation_differences"] = {n: {k: (round(v, 5) if isinstance(v, float) else v)
+                                                           for k, v in flips[n].items()} for n in keep}
+            del shared, free
             if world == 1:
                 per_block = model.compare_blocks(latent, 500.0, text)
                 checks["per_block_same_input_cosine_min"] = min(c for c, _ in per_block)

@@ -232,6 +232,16 @@ class FP4Tensor:
         self._gscale = global_scale.contiguous().reshape(1)
         return self
 
+    def snapshot(self) -> "FP4Tensor":
+        """A second handle on the same packed buffers with its own copy of the amax / tensor-scale
+        slots (additive; callers that keep a packed tensor while its producer reuses those
+        one-element slots for the next tensor)."""
+        other = object.__new__(FP4Tensor)
+        for name in self.__slots__:
+            setattr(other, name, getattr(self, name))
+        other._amax, other._gscale = self._amax.clone(), self._gscale.clone()
+        return other
+
     # ------------------------------------------------------------ access --
     def to_bfloat16(self) -> torch.Tensor:
         """Dequantize (fx/src/s4/nvfp4/tensor.h:53-72)."""

@@ -222,7 +222,8 @@ NVFP4_API int64_t nvfp4_exchange_sync_bytes(void);
  * epoch, i.e. until all ranks' producer kernels of this exchange have finished storing.  One
  * tiny kernel that polls with plain loads; limit_ns bounds the wait: when it runs out the
  * kernel stores 0xB00 + (the first missing rank) in *status_dev (nullable) and returns
- * normally -- the GPU is never left spinning.  For kind 1, amax_out_dev (nullable) receives the
+ * normally -- the GPU is never left spinning; while *status_dev stays non-zero later waits
+ * return at once, so a missing rank costs one limit per step, not one per exchange.  For kind 1, amax_out_dev (nullable) receives the
  * tensor amax of the assembled attention output (the maximum over the sources' partial maxima),
  * ready for nvfp4_quantize_bf16.  No reference counterpart. */
 NVFP4_API int nvfp4_exchange_wait(void* sync_block, int kind, int world, int64_t limit_ns,

@@ -119,6 +119,13 @@ def test_wait_runs_out_and_reports_the_missing_rank():
     rc = N.lib.nvfp4_exchange_wait(sync[0].data_ptr(), 0, world, 3_000_000, None, status.data_ptr(), st)
     torch.cuda.synchronize()
     assert rc == 0 and int(status.item()) == 0xB01
+    # while the status word stays set, a further wait on a missing flag returns at once
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    assert N.lib.nvfp4_exchange_wait(sync[0].data_ptr(), 0, world, 2_000_000_000, None,
+                                     status.data_ptr(), st) == 0
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 0.5 and int(status.item()) == 0xB01
     # bad arguments are refused on the host
     assert N.lib.nvfp4_exchange_wait(None, 0, world, 1000, None, None, st) == 1
     assert N.lib.nvfp4_exchange_wait(sync[0].data_ptr(), 2, world, 1000, None, None, st) == 1
