@@ -4,6 +4,7 @@
     python -m blackwell_diffusion_rtx6000_5090_i2v_b200.profile_case quantize --m 27280 --k 3072
     python -m blackwell_diffusion_rtx6000_5090_i2v_b200.profile_case norm --m 27280 --k 3072
     python -m blackwell_diffusion_rtx6000_5090_i2v_b200.profile_case rope --m 27280 --k 3072
+    python -m blackwell_diffusion_rtx6000_5090_i2v_b200.profile_case return --m 32760 --k 5120
 
 Each case holds well under a few GB on the device, launches the kernel
 ``--iters`` times after ``--warmup`` launches, and prints the CUDA-event time.
@@ -34,7 +35,8 @@ def _time(fn, warmup, iters):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "quantize", "amax", "norm", "rope"])
+    ap.add_argument("kernel", choices=["gemm", "quantize", "amax", "norm", "rope", "return"])
+    ap.add_argument("--tiling", choices=["auto", "uniform", "alternating"], default="auto")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=9216)
     ap.add_argument("--k", type=int, default=3072)
@@ -49,6 +51,8 @@ def main():
     x = student_t_bf16((a.m, a.k), 7, device="cuda")
     st = torch.cuda.current_stream().cuda_stream
     if a.kernel == "gemm":
+        from .nvfp4 import set_gemm_tiling
+        set_gemm_tiling(a.tiling)
         w = outlier_weight_bf16((a.n, a.k), 8, device="cuda")
         qa = FP4Tensor.from_bfloat16(x, linear_scales=False)
         qb = FP4Tensor.from_bfloat16(w, linear_scales=False)
@@ -74,6 +78,28 @@ def main():
         N.check_status()
         nbytes = 2 * (2.0 + 2.0) * a.m * a.k          # q and k, read + written
         print(f"qk_norm_rope [{a.m}, 3x{a.k}]: {ms:.4f} ms, {nbytes / ms / 1e6:.1f} GB/s")
+    elif a.kernel == "return":
+        # the attention-output return exchange on one GPU (one rank: every store is local), then
+        # the flag wait that also reduces the amax: [m, k/128 heads, 128] -> the same buffer layout
+        import ctypes
+        heads = a.k // 128
+        o = x.view(a.m, heads, 128)
+        out = torch.empty_like(o)
+        sync = torch.zeros(N.lib.nvfp4_exchange_sync_bytes() // 4, dtype=torch.int32, device="cuda")
+        amax = torch.zeros(1, device="cuda")
+        outs = (ctypes.c_void_p * 1)(out.data_ptr())
+        syncs = (ctypes.c_void_p * 1)(sync.data_ptr())
+
+        def run():
+            N.check(N.lib.nvfp4_attn_return_exchange_bf16(o.data_ptr(), o.stride(0), o.stride(1), a.m,
+                                                          heads, 128, outs, syncs, 1, 0, st), "return")
+            N.check(N.lib.nvfp4_exchange_wait(sync.data_ptr(), 1, 1, 1_000_000_000, amax.data_ptr(),
+                                              N.ptr(N.status_word(x.device)), st), "wait")
+        ms = _time(run, a.warmup, a.iters)
+        N.check_status()
+        assert torch.equal(out, o) and float(amax) == float(o.abs().max())
+        print(f"attention return [{a.m}, {heads}, 128]: {ms:.4f} ms, {4.0 * a.m * a.k / ms / 1e6:.1f} GB/s "
+              "(read + write)")
     elif a.kernel == "norm":
         # LayerNorm + adaLN modulation + quantize: both sweeps per iteration
         g = torch.Generator(device="cuda").manual_seed(9)

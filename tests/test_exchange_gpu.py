@@ -37,6 +37,13 @@ def _worker(rank, world, port, out):
         nvfp4.check_status()
         assert torch.isfinite(a.float()).all()
         assert torch.equal(a, b) and torch.equal(b, c)
+        # every quantizer's amax all-reduced (max) over the shards: the sharded step quantizes
+        # with the unsharded model's tensor scales and reproduces its output
+        d = model.forward(latent, 500.0, text, group=grp, exchange="peer", amax_sync=True)
+        full = model.forward(latent, 500.0, text)
+        nvfp4.check_status()
+        cos = torch.dot(d.double().flatten(), full.double().flatten()) / (d.double().norm() * full.double().norm())
+        assert float(cos) >= 1 - 1e-9, float(cos)
         out[rank] = 1
     finally:
         dist.destroy_process_group()

@@ -46,6 +46,11 @@ def _worker(rank, world, port, L, H, D, out):
         assert torch.allclose(o_local, ref[sl], atol=1e-5, rtol=1e-5)
         # round trip
         assert torch.equal(ulysses.heads_to_seq(ulysses.seq_to_heads(q[sl].contiguous())), q[sl])
+        # the send buffer already grouped by destination rank (the layout the q/k norm + RoPE
+        # kernel writes in its exchange form): one collective, no packing copy
+        packed = torch.cat([q[sl], k[sl], v[sl]], dim=-1)                    # [Lp, H, 3D]
+        send = packed.reshape(Lp, world, Hp, 3 * D).permute(1, 0, 2, 3).contiguous()
+        assert torch.equal(ulysses.all_to_all_packed(send, dist.group.WORLD), qkv)
         # bad head count is refused before any communication
         try:
             ulysses.seq_to_heads(torch.zeros(Lp, H + 1, D))
