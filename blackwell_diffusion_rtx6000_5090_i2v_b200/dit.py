@@ -288,13 +288,16 @@ def qk_norm_rope(qkv: torch.Tensor, heads: int, head_dim: int, gain_q: Optional[
 
 def rms_norm_fused(x: torch.Tensor, heads: int, head_dim: int, gain: Optional[torch.Tensor],
                    eps: float) -> torch.Tensor:
-    """RMSNorm over the last axis of a contiguous bf16 ``[L, heads*head_dim]`` tensor with the
-    same kernel (no rotation); returns ``[L, heads, head_dim]``."""
+    """RMSNorm over the last axis of a bf16 ``[L, heads*head_dim]`` tensor (rows may be a strided
+    view, e.g. a column block of a wider matrix) with the same kernel (no rotation); returns a
+    contiguous ``[L, heads, head_dim]``."""
     L, dim = x.shape
-    if dim != heads * head_dim or x.dtype != torch.bfloat16 or not x.is_contiguous():
-        raise RuntimeError("rms_norm_fused: x must be a contiguous bf16 [L, heads*head_dim] tensor")
+    if dim != heads * head_dim or x.dtype != torch.bfloat16 or x.stride(1) != 1 or \
+            x.stride(0) % 8 != 0 or x.data_ptr() % 16 != 0:
+        raise RuntimeError("rms_norm_fused: x must be a bf16 [L, heads*head_dim] tensor with unit "
+                           "inner stride and 16-byte aligned rows")
     out = torch.empty(L, heads, head_dim, dtype=torch.bfloat16, device=x.device)
-    N.check(N.lib.nvfp4_qk_norm_rope_bf16(x.data_ptr(), None, None, dim, L, heads, head_dim,
+    N.check(N.lib.nvfp4_qk_norm_rope_bf16(x.data_ptr(), None, None, x.stride(0), L, heads, head_dim,
                                           N.ptr(gain), None, float(eps), None, out.data_ptr(), None,
                                           None, dim, head_dim, N.ptr(N.status_word(x.device)),
                                           N.stream_ptr()), "rms_norm")
@@ -410,13 +413,16 @@ class WanBlock:
               if mode == "nvfp4" else self.cross_kv.dequant(ctx, reorder=mode == "dequant_reordered"))
         return self._split_text_kv(kv)
 
-    def _split_text_kv(self, kv: torch.Tensor):
-        """``[C, 2*dim]`` projection of the text context -> normalised k and v, ``[C, heads, D]``."""
+    def _split_text_kv(self, kv: torch.Tensor, fused: bool = False):
+        """``[C, 2*dim]`` projection of the text context -> normalised k and v, ``[C, heads, D]``.
+        ``fused``: the RMSNorm of k by the library's kernel (one launch, straight off the column
+        block of the stacked projection) instead of the separate torch ops."""
         cfg = self.cfg
         k, v = kv.chunk(2, dim=-1)
         C = kv.shape[0]
-        return (rms_norm(k, self.g_ck, cfg.eps).view(C, cfg.heads, cfg.head_dim),
-                v.reshape(C, cfg.heads, cfg.head_dim))
+        kn = (rms_norm_fused(k, cfg.heads, cfg.head_dim, self.g_ck, cfg.eps) if fused
+              else rms_norm(k, self.g_ck, cfg.eps).view(C, cfg.heads, cfg.head_dim))
+        return kn, v.reshape(C, cfg.heads, cfg.head_dim)
 
     # -------------------------------------------------------------- forward --
     def forward(self, x: torch.Tensor, ctx: torch.Tensor, temb6: torch.Tensor, cos, sin,
@@ -590,7 +596,8 @@ class WanDiT:
         for blk in self.blocks:
             _record_amax(blk.cross_kv, ctx_q)
         kv = self.text_kv.gemm(ctx_q)
-        return [blk._split_text_kv(kv[:, i * two_d:(i + 1) * two_d]) for i, blk in enumerate(self.blocks)]
+        return [blk._split_text_kv(kv[:, i * two_d:(i + 1) * two_d], fused=True)
+                for i, blk in enumerate(self.blocks)]
 
     def forward(self, latent: torch.Tensor, t: float, text: torch.Tensor, mode: str = "nvfp4",
                 group: Optional[dist.ProcessGroup] = None, exchange: str = "nccl",
