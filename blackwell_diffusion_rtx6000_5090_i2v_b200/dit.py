@@ -38,7 +38,7 @@ import torch.nn.functional as F
 
 from . import _native as N
 from . import ulysses
-from .nvfp4 import FP4Tensor, StackedWeights, fp4_gemm
+from .nvfp4 import FP4Tensor, PackedBuffers, StackedWeights, fp4_gemm
 
 
 @dataclass(frozen=True)
@@ -320,6 +320,22 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor
     return o.squeeze(0).transpose(0, 1)
 
 
+class ActivationScratch:
+    """Packed-activation buffers of a step, one set per activation shape: every quantizer of the
+    block loop writes into them instead of allocating (the ``out=`` form; the block-linears
+    runner preallocates the same way)."""
+
+    def __init__(self, device):
+        self.device = device
+        self._bufs: Dict[Tuple[int, int], PackedBuffers] = {}
+
+    def get(self, rows: int, cols: int) -> PackedBuffers:
+        key = (rows, cols)
+        if key not in self._bufs:
+            self._bufs[key] = PackedBuffers(rows, cols, self.device)
+        return self._bufs[key]
+
+
 class WanBlock:
     def __init__(self, cfg: WanDiTConfig, gen: torch.Generator, device, name: str = "block"):
         d = cfg.dim
@@ -428,12 +444,13 @@ class WanBlock:
     def forward(self, x: torch.Tensor, ctx: torch.Tensor, temb6: torch.Tensor, cos, sin,
                 mode: str = "nvfp4", group=None, cos_sin: Optional[torch.Tensor] = None,
                 px: Optional[ulysses.PeerExchange] = None, text_kv=None,
-                amax_hook=None) -> torch.Tensor:
+                amax_hook=None, scratch: Optional["ActivationScratch"] = None) -> torch.Tensor:
         """``text_kv``: this block's cross-attention ``(k, v)`` when the step computed them
         for all blocks ahead of the loop.  ``amax_hook(t)``: called on every activation's
         one-element amax tensor between the amax pass and the packing pass (sharded runs use it
         to all-reduce the maximum, which makes every shard quantize with the full tensor's
-        scale)."""
+        scale).  ``scratch``: preallocated buffers for the packed activations (shared by all
+        blocks of a step: each packed activation is consumed by the GEMM that follows it)."""
         cfg = self.cfg
         mod = self.scale_shift_table + temb6.float()
         shift_msa, scale_msa, gate_msa, c_shift, c_scale, c_gate = (m.contiguous() for m in mod)
@@ -443,9 +460,12 @@ class WanBlock:
                 cos_sin = pack_rope_table(cos, sin)
             _mark("other")
             ls = _want_linear_scales()
+            # a recording keeps the packed tensors, so it gets fresh ones
+            buf = (lambda t, cols: scratch.get(t.shape[0], cols)) if scratch is not None and not ls \
+                else (lambda t, cols: None)
             a = _record_amax(self.qkv, FP4Tensor.from_norm_mod(x, scale=scale_msa, shift=shift_msa,
                                                                eps=cfg.eps, amax_hook=amax_hook,
-                                                               linear_scales=ls))
+                                                               linear_scales=ls, out=buf(x, cfg.dim)))
             _mark("norm_quantize")
             qkv = self.qkv.nvfp4(a)
             _mark("gemm_qkv")
@@ -455,13 +475,13 @@ class WanBlock:
             # with the peer exchange the return kernel has already taken max|o|
             oq = _record_amax(self.attn_out, FP4Tensor.from_bfloat16(
                 o.contiguous(), linear_scales=ls, amax=o_amax,
-                amax_hook=None if o_amax is not None else amax_hook))
+                amax_hook=None if o_amax is not None else amax_hook, out=buf(o, cfg.dim)))
             _mark("quantize")
             x = self.attn_out.nvfp4(oq, gate=gate_msa, C=x, beta=1.0)
             _mark("gemm_attn_out")
             a = _record_amax(self.cross_q, FP4Tensor.from_norm_mod(
                 x, weight=self.norm2_w, bias=self.norm2_b, eps=cfg.eps, amax_hook=amax_hook,
-                linear_scales=ls))
+                linear_scales=ls, out=buf(x, cfg.dim)))
             _mark("norm_quantize")
             q = self.cross_q.nvfp4(a)
             _mark("gemm_cross_q")
@@ -474,20 +494,22 @@ class WanBlock:
             o = attention(q, ck, cv).reshape(L, cfg.dim)
             _mark("cross_attention")
             oq = _record_amax(self.cross_out, FP4Tensor.from_bfloat16(o.contiguous(), linear_scales=ls,
-                                                                      amax_hook=amax_hook))
+                                                                      amax_hook=amax_hook,
+                                                                      out=buf(o, cfg.dim)))
             _mark("quantize")
             x = self.cross_out.nvfp4(oq, C=x, beta=1.0)
             _mark("gemm_cross_out")
             a = _record_amax(self.ffn_up, FP4Tensor.from_norm_mod(x, scale=c_scale, shift=c_shift,
                                                                   eps=cfg.eps, amax_hook=amax_hook,
-                                                                  linear_scales=ls))
+                                                                  linear_scales=ls, out=buf(x, cfg.dim)))
             _mark("norm_quantize")
             hid = self.ffn_up.nvfp4(a, gelu=True, out_amax=self._amax)
             _mark("gemm_ffn_up")
             if amax_hook is not None:
                 amax_hook(self._amax)
             hq = _record_amax(self.ffn_down, FP4Tensor.from_bfloat16(hid, linear_scales=ls,
-                                                                     amax=self._amax))
+                                                                     amax=self._amax,
+                                                                     out=buf(hid, cfg.ffn)))
             _mark("quantize")
             x = self.ffn_down.nvfp4(hq, gate=c_gate, C=x, beta=1.0)
             _mark("gemm_ffn_down")
@@ -537,6 +559,7 @@ class WanDiT:
                         if (2 * d) % 256 == 0 and self.blocks else None)
         self._rope: Dict[Tuple[int, int, int], Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = {}
         self._px: Dict[Tuple[int, int], ulysses.PeerExchange] = {}
+        self._scratch = ActivationScratch(self.device)
         self.out_table = torch.randn(2, d, generator=gen, device=self.device) / d ** 0.5
         self.proj_out = PackedLinear(cfg.out_channels * pt * ph * pw, d, gen, self.device, name="proj_out")
 
@@ -636,7 +659,7 @@ class WanDiT:
             _mark("text_kv")
         for i, blk in enumerate(self.blocks):
             x = blk.forward(x, ctx, temb6, cos, sin, mode, group if P > 1 else None, cos_sin, px,
-                            kvs[i] if kvs is not None else None, hook)
+                            kvs[i] if kvs is not None else None, hook, self._scratch)
         y = self._head(x, temb, mode, hook)
         if P > 1:
             parts = [torch.empty_like(y) for _ in range(P)]

@@ -61,6 +61,32 @@ def _require_block_1d(mode: QuantizationMode, what: str) -> None:
         raise RuntimeError(f"{pretty} {what} not yet implemented in clean version")
 
 
+class PackedBuffers:
+    """Preallocated device buffers for the packed form of a bf16 ``[rows, cols]`` activation
+    (additive: the ``out=`` form of the quantizers; the reference allocates on every call,
+    fx/src/s4/nvfp4/tensor.cpp:7-16, kernel.cu:109-110,140-142).  A quantizer given one writes
+    into it and returns an :class:`FP4Tensor` that aliases it; the caller keeps that tensor only
+    until the next quantizer call with the same buffers."""
+
+    def __init__(self, rows: int, cols: int, device, linear_scales: bool = False):
+        if cols % FP4_BLOCK_SIZE != 0:
+            raise RuntimeError("[s4] [nvfp4] [tensor] cols must be a multiple of 16")
+        self.rows, self.cols, self.device = rows, cols, torch.device(device)
+        with torch.cuda.device(self.device):
+            self.data = torch.empty(rows * cols // 2, dtype=torch.uint8, device=self.device)
+            self.scales_swz = torch.empty(N.lib.nvfp4_swizzled_scale_bytes(rows, cols), dtype=torch.uint8,
+                                          device=self.device)
+            self.scales = (torch.empty(rows * cols // FP4_BLOCK_SIZE, dtype=torch.uint8, device=self.device)
+                           if linear_scales else None)
+            self.amax = torch.empty(1, dtype=torch.float32, device=self.device)
+            self.gscale = torch.empty(1, dtype=torch.float32, device=self.device)
+            self.stats = torch.empty(rows, 2, dtype=torch.float32, device=self.device)   # fused norm
+        self.device = self.data.device       # with its index, as tensors report it
+
+    def matches(self, rows: int, cols: int, device) -> bool:
+        return (rows, cols) == (self.rows, self.cols) and torch.device(device) == self.device
+
+
 class FP4Tensor:
     """Owning packed NVFP4 tensor (fx/src/s4/nvfp4/tensor.h:22-115).
 
@@ -82,11 +108,14 @@ class FP4Tensor:
     def from_bfloat16(input: torch.Tensor,
                       mode: QuantizationMode = QuantizationMode.block_1d,
                       *, linear_scales: bool = True, swizzled_scales: bool = True,
-                      amax: Optional[torch.Tensor] = None, amax_hook=None) -> "FP4Tensor":
+                      amax: Optional[torch.Tensor] = None, amax_hook=None,
+                      out: Optional[PackedBuffers] = None) -> "FP4Tensor":
         """``amax`` (additive): a one-element fp32 device tensor already holding max|input|,
         e.g. from the GEMM that produced ``input``; the amax pass is then skipped.
         ``amax_hook`` (additive): called with the amax tensor between the amax pass and the
-        packing pass, e.g. to all-reduce the maximum over the shards of a sharded tensor."""
+        packing pass, e.g. to all-reduce the maximum over the shards of a sharded tensor.
+        ``out`` (additive): preallocated buffers of the input's ``[rows, cols]``; nothing is
+        allocated and the result aliases them."""
         if input.dtype != torch.bfloat16:
             raise RuntimeError("[s4] [nvfp4] [tensor] Input must be BFloat16")
         if not input.is_cuda:
@@ -116,15 +145,23 @@ class FP4Tensor:
                                      or amax.device != dev):
                 raise RuntimeError("[s4] [nvfp4] [tensor] amax must be a one-element float32 "
                                    "tensor on the input's device")
-            self._amax = amax if amax is not None else torch.empty(1, dtype=torch.float32,
-                                                                   device=dev)
-            self._gscale = torch.empty(1, dtype=torch.float32, device=dev)
-            self._data = torch.empty(rows * cols // 2, dtype=torch.uint8, device=dev)
-            self._scales = (torch.empty(rows * cols // FP4_BLOCK_SIZE, dtype=torch.uint8, device=dev)
-                            if linear_scales else None)
-            self._scales_swz = (torch.empty(N.lib.nvfp4_swizzled_scale_bytes(rows, cols),
-                                            dtype=torch.uint8, device=dev)
-                                if swizzled_scales and rows * cols > 0 else None)
+            if out is not None:
+                if not out.matches(rows, cols, dev) or (linear_scales and out.scales is None):
+                    raise RuntimeError("[s4] [nvfp4] [tensor] out buffers do not match the input")
+                self._amax = amax if amax is not None else out.amax
+                self._gscale, self._data = out.gscale, out.data
+                self._scales = out.scales if linear_scales else None
+                self._scales_swz = out.scales_swz
+            else:
+                self._amax = amax if amax is not None else torch.empty(1, dtype=torch.float32,
+                                                                       device=dev)
+                self._gscale = torch.empty(1, dtype=torch.float32, device=dev)
+                self._data = torch.empty(rows * cols // 2, dtype=torch.uint8, device=dev)
+                self._scales = (torch.empty(rows * cols // FP4_BLOCK_SIZE, dtype=torch.uint8, device=dev)
+                                if linear_scales else None)
+                self._scales_swz = (torch.empty(N.lib.nvfp4_swizzled_scale_bytes(rows, cols),
+                                                dtype=torch.uint8, device=dev)
+                                    if swizzled_scales and rows * cols > 0 else None)
             st = N.stream_ptr()
             if amax is None:
                 N.check(N.lib.nvfp4_amax_bf16(N.ptr(x), rows * cols, N.ptr(self._amax), st),
@@ -141,7 +178,8 @@ class FP4Tensor:
     def from_norm_mod(x: torch.Tensor, *, weight: Optional[torch.Tensor] = None,
                       bias: Optional[torch.Tensor] = None, scale: Optional[torch.Tensor] = None,
                       shift: Optional[torch.Tensor] = None, rms: bool = False, eps: float = 1e-6,
-                      linear_scales: bool = False, return_normed: bool = False, amax_hook=None):
+                      linear_scales: bool = False, return_normed: bool = False, amax_hook=None,
+                      out: Optional[PackedBuffers] = None):
         """Quantize ``bf16(norm(x) * weight + bias) * (1 + scale) + shift`` without ever
         writing that tensor: the fused producer in front of the DiT block's linears
         (fx/src/s4/models/wan22/wan_transformer.py:204-206,210,218-220).  ``x`` is bf16
@@ -172,14 +210,21 @@ class FP4Tensor:
         self._rows, self._cols = rows, cols
         with torch.cuda.device(dev):
             xc = x.contiguous()
-            self._amax = torch.empty(1, dtype=torch.float32, device=dev)
-            self._gscale = torch.empty(1, dtype=torch.float32, device=dev)
-            self._data = torch.empty(rows * cols // 2, dtype=torch.uint8, device=dev)
-            self._scales = (torch.empty(rows * cols // FP4_BLOCK_SIZE, dtype=torch.uint8, device=dev)
-                            if linear_scales else None)
-            self._scales_swz = torch.empty(N.lib.nvfp4_swizzled_scale_bytes(rows, cols),
-                                           dtype=torch.uint8, device=dev)
-            stats = torch.empty(rows, 2, dtype=torch.float32, device=dev)
+            if out is not None:
+                if not out.matches(rows, cols, dev) or (linear_scales and out.scales is None):
+                    raise RuntimeError("[s4] [nvfp4] [tensor] out buffers do not match the input")
+                self._amax, self._gscale, self._data = out.amax, out.gscale, out.data
+                self._scales = out.scales if linear_scales else None
+                self._scales_swz, stats = out.scales_swz, out.stats
+            else:
+                self._amax = torch.empty(1, dtype=torch.float32, device=dev)
+                self._gscale = torch.empty(1, dtype=torch.float32, device=dev)
+                self._data = torch.empty(rows * cols // 2, dtype=torch.uint8, device=dev)
+                self._scales = (torch.empty(rows * cols // FP4_BLOCK_SIZE, dtype=torch.uint8, device=dev)
+                                if linear_scales else None)
+                self._scales_swz = torch.empty(N.lib.nvfp4_swizzled_scale_bytes(rows, cols),
+                                               dtype=torch.uint8, device=dev)
+                stats = torch.empty(rows, 2, dtype=torch.float32, device=dev)
             normed = torch.empty_like(xc) if return_normed else None
             st = N.stream_ptr()
             status = N.ptr(N.status_word(dev))

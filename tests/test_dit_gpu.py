@@ -226,3 +226,30 @@ def test_full_width_step_parity_statements():
     assert c_shared >= 0.999, c_shared
     assert c_free >= 0.98 and (1 - c_free) <= 1.5 * (1 - c_ctl) + 1e-3, (c_free, c_ctl)
     assert abs(c_pin - c_free) <= 5e-3, (c_pin, c_free)
+
+
+def test_preallocated_packed_buffers_change_nothing(small):
+    """The ``out=`` form of the quantizers (buffers shared by all blocks of a step) against the
+    allocating form: same bits, and the buffers really are reused."""
+    from blackwell_diffusion_rtx6000_5090_i2v_b200 import nvfp4
+    from blackwell_diffusion_rtx6000_5090_i2v_b200.nvfp4 import FP4Tensor, PackedBuffers
+    dit, model, latent, text = small
+    x, cos, sin, cos_sin, temb, temb6, ctx, grid = model._embed(latent, 500.0, text, "nvfp4")
+    blk = model.blocks[0]
+    scratch = dit.ActivationScratch(x.device)
+    y0 = blk.forward(x, ctx, temb6, cos, sin, "nvfp4", None, cos_sin)
+    y1 = blk.forward(x, ctx, temb6, cos, sin, "nvfp4", None, cos_sin, scratch=scratch)
+    y2 = blk.forward(x, ctx, temb6, cos, sin, "nvfp4", None, cos_sin, scratch=scratch)
+    nvfp4.check_status()
+    assert torch.equal(y0, y1) and torch.equal(y1, y2)
+    assert set(scratch._bufs) == {(x.shape[0], model.cfg.dim), (x.shape[0], model.cfg.ffn)}
+    # the quantizer itself: out= aliases the given buffers and refuses a wrong shape
+    bufs = PackedBuffers(x.shape[0], model.cfg.dim, x.device, linear_scales=True)
+    t = FP4Tensor.from_bfloat16(x, out=bufs)
+    ref = FP4Tensor.from_bfloat16(x)
+    assert t.quantized_data().data_ptr() == bufs.data.data_ptr()
+    assert torch.equal(t.quantized_data(), ref.quantized_data())
+    assert torch.equal(t.scale_factors(), ref.scale_factors())
+    assert torch.equal(t.scale_factors_swizzled(), ref.scale_factors_swizzled())
+    with pytest.raises(RuntimeError, match="do not match"):
+        FP4Tensor.from_bfloat16(x[:-1].contiguous(), out=bufs)
