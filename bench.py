@@ -204,7 +204,7 @@ def run_reference(args, rank: int):
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
-        "native_library_loaded": any("_native" in m for m in sys.modules),
+        "native_library_loaded": "blackwell_diffusion_rtx6000_5090_i2v_b200._native" in sys.modules,
     }
     print(json.dumps(line), flush=True)
 
