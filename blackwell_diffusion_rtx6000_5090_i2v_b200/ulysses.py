@@ -96,7 +96,7 @@ class PeerExchange:
     """
 
     def __init__(self, tokens_total: int, heads: int, head_dim: int, group: dist.ProcessGroup,
-                 device: torch.device, wait_limit_s: float = 10.0):
+                 device: torch.device, wait_limit_s: float = 30.0):
         import ctypes
         import os
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
