@@ -77,3 +77,43 @@ def test_single_rank_is_identity():
     assert ulysses.seq_to_heads(x) is x and ulysses.heads_to_seq(x) is x
     # A14B shape at 8 ranks: 4 tensors of 4095 tokens x 40 heads x 128 x 2 B, 7/8 of which leave
     assert ulysses.exchange_bytes_per_rank(32760, 40, 128, 8) == 4 * 4095 * 40 * 128 * 2 * 7 // 8
+
+
+def _leaver(rank, world, port, out):
+    """Rank 1 leaves between steps (no collective of its own in flight); rank 0's next exchange
+    must end with an error inside the group's time limit instead of hanging."""
+    import datetime
+    import time
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    from blackwell_diffusion_rtx6000_5090_i2v_b200 import ulysses
+    x = torch.randn(4, 4, 8)
+    ulysses.seq_to_heads(x)                     # one healthy step on both ranks
+    if rank == 1:
+        out[1] = "left"
+        os._exit(0)                             # gone: no goodbye, no destroy
+    t0 = time.perf_counter()
+    try:
+        ulysses.seq_to_heads(x)
+        out[0] = "no error"
+    except Exception as e:                      # gloo reports the closed connection or the timeout
+        out[0] = f"error after {time.perf_counter() - t0:.1f}s: {type(e).__name__}"
+    os._exit(0)
+
+
+def test_departed_rank_surfaces_as_error_not_a_hang():
+    port = _free_port()
+    out = mp.Manager().dict()
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=_leaver, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=60)
+    alive = [p for p in procs if p.is_alive()]
+    for p in alive:
+        p.kill()
+    assert not alive, "a rank hung after its peer left"
+    assert out.get(1) == "left"
+    assert str(out.get(0, "")).startswith("error after"), out.get(0)
