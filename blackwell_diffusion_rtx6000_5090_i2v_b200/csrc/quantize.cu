@@ -203,6 +203,8 @@ int zero_swizzle_padding(uint8_t* swz, int64_t rows, int64_t cols, cudaStream_t 
 int quantize_impl(const void* x, int64_t rows, int64_t cols, const float* amax_dev, float amax_val,
                   uint8_t* packed, uint8_t* sf_lin, uint8_t* sf_swz, float* gscale, void* stream) {
   if (rows < 0 || cols < 0 || cols % kBlock != 0) return NVFP4_ERR_BAD_ARG;
+  // each extent first, so that the product cannot wrap; then at most 2^31 - 1 scale blocks
+  if (rows >= ((int64_t)1 << 31) || cols >= ((int64_t)1 << 31)) return NVFP4_ERR_BAD_ARG;
   const int64_t n_blocks = rows * cols / kBlock;
   if (n_blocks >= (int64_t)1 << 31) return NVFP4_ERR_BAD_ARG;
   if (n_blocks == 0) return NVFP4_OK;
@@ -274,7 +276,7 @@ int nvfp4_quantize_bf16_amax(const void* x, uint8_t* packed, uint8_t* scales, in
 
 static int dequantize_impl(const uint8_t* packed, const uint8_t* scales, int64_t n,
                            const float* amax_dev, float amax_val, void* out, void* stream) {
-  if (n < 0 || n % kBlock != 0) return NVFP4_ERR_BAD_ARG;
+  if (n < 0 || n % kBlock != 0 || n / kBlock >= ((int64_t)1 << 31)) return NVFP4_ERR_BAD_ARG;
   if (n == 0) return NVFP4_OK;
   if (!packed || !scales || !out) return NVFP4_ERR_BAD_ARG;
   if ((reinterpret_cast<uintptr_t>(packed) & 3u) || !aligned16(out)) return NVFP4_ERR_BAD_ALIGN;
@@ -291,6 +293,7 @@ static int dequantize_impl(const uint8_t* packed, const uint8_t* scales, int64_t
 int nvfp4_dequantize_bf16(const uint8_t* packed, const uint8_t* scales_linear, int64_t rows,
                           int64_t cols, const float* amax_dev, void* out_bf16, void* stream) {
   if (rows < 0 || cols < 0 || cols % kBlock != 0 || !amax_dev) return NVFP4_ERR_BAD_ARG;
+  if (rows >= ((int64_t)1 << 31) || cols >= ((int64_t)1 << 31)) return NVFP4_ERR_BAD_ARG;
   return dequantize_impl(packed, scales_linear, rows * cols, amax_dev, 0.0f, out_bf16,
                          stream);
 }
@@ -303,7 +306,9 @@ int nvfp4_dequantize_bf16_amax(const uint8_t* packed, const uint8_t* scales, voi
 int nvfp4_swizzle_scales(const uint8_t* scales_linear, int64_t rows, int64_t cols,
                          uint8_t* scales_swizzled, void* stream) {
   if (rows < 0 || cols < 0 || cols % kBlock != 0) return NVFP4_ERR_BAD_ARG;
+  if (rows >= ((int64_t)1 << 31) || cols >= ((int64_t)1 << 31)) return NVFP4_ERR_BAD_ARG;
   const int64_t n_sf = rows * cols / kBlock;
+  if (n_sf >= (int64_t)1 << 32) return NVFP4_ERR_BAD_ARG;      // the grid would not fit
   if (n_sf == 0) return NVFP4_OK;
   if (!scales_linear || !scales_swizzled) return NVFP4_ERR_BAD_ARG;
   int rc = check_device_sm100();

@@ -57,6 +57,10 @@ def test_argument_validation_without_device():
     assert L.nvfp4_gemm(None, None, None, None, None, None, 0, 16, 64, 1.0, 0.0, None, None,
                         None, 0, None, None, None, None) == 0  # empty problem is a no-op
     assert L.nvfp4_amax_bf16(None, 16, None, None) == 1
+    # extents whose product would wrap a 64-bit integer are refused before anything is multiplied
+    assert L.nvfp4_quantize_bf16(None, 1 << 40, 1 << 40, None, None, None, None, None, None) == 1
+    assert L.nvfp4_dequantize_bf16(None, None, 1 << 40, 1 << 40, None, None, None) == 1
+    assert L.nvfp4_swizzle_scales(None, 1 << 40, 1 << 40, None, None) == 1
     # the fused norm quantizer stores 8-byte words of nibbles: a packed pointer that is only
     # 4-byte aligned is refused on the host (status 2), nothing is launched
     fake = 0x10000
