@@ -58,11 +58,13 @@ def test_return_exchange_layout_amax_and_flags(world, L, Hp, D, transposed):
             assert float(amax[s].item()) == float(want.float().abs().max().item()), (rnd, s)
 
 
-def test_rope_exchange_raises_flags_and_wait_passes():
-    """The q/k norm + RoPE kernel in its exchange form with sync blocks, two emulated ranks: the
-    pieces equal the plain packed form's, and the kind-0 wait passes on both ranks."""
+@pytest.mark.parametrize("world,heads,Lp", [(2, 4, 150), (4, 8, 33), (8, 40, 9)])
+def test_rope_exchange_raises_flags_and_wait_passes(world, heads, Lp):
+    """The q/k norm + RoPE kernel in its exchange form with sync blocks, 2 / 4 / 8 emulated ranks
+    (odd token counts per rank, five heads per rank as in the 8-GPU A14B run): the pieces equal
+    the plain packed form's, and the kind-0 wait passes on every rank."""
     from blackwell_diffusion_rtx6000_5090_i2v_b200 import dit
-    world, heads, D, Lp = 2, 4, 128, 150
+    D = 128
     N, sync, sync_ptrs = _setup(world)
     L, Hp, dim = world * Lp, heads // world, heads * D
     cfg = dit.WanDiTConfig(dim=dim, heads=heads, ffn=1024, layers=1, in_channels=16, out_channels=16)
