@@ -262,7 +262,8 @@ int64_t nvfp4_swizzled_scale_bytes(int64_t rows, int64_t cols) {
 int nvfp4_quantize_bf16(const void* x, int64_t rows, int64_t cols, const float* amax_dev,
                         uint8_t* packed, uint8_t* scales_linear, uint8_t* scales_swizzled,
                         float* global_scale_dev, void* stream) {
-  if (!amax_dev) return NVFP4_ERR_BAD_ARG;
+  // an empty tensor reads nothing, not even the amax slot
+  if (!amax_dev && rows > 0 && cols > 0) return NVFP4_ERR_BAD_ARG;
   return quantize_impl(x, rows, cols, amax_dev, 0.0f, packed, scales_linear, scales_swizzled,
                        global_scale_dev, stream);
 }
