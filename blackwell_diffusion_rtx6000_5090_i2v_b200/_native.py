@@ -49,6 +49,8 @@ SIGNATURES = {
     "nvfp4_exchange_sync_bytes": (_i64, []),
     "nvfp4_exchange_wait": (_i, [_p, _i, _i, _i64, _p, _p, _p]),
     "nvfp4_attn_return_exchange_bf16": (_i, [_p, _i64, _i64, _i64, _i, _i, _p, _p, _i, _i, _p]),
+    "nvfp4_attention_bf16": (_i, [_p, _i64, _i64, _p, _i64, _i64, _p, _i64, _i64, _i64, _i64, _i, _i, _f,
+                                  _p, _i64, _i64, _p, _p, _p]),
     "nvfp4_linear_bf16_static": (_i, [_p, _i64, _i64, _p, _p, _p, _i64, _p, _i, _p, _p, _p]),
     "nvfp4_linear_bf16_static_max_elements": (_i64, []),
 }

@@ -313,8 +313,34 @@ def layer_norm(x: torch.Tensor, eps: float, weight=None, bias=None) -> torch.Ten
     return F.layer_norm(x.float(), (x.shape[-1],), weight, bias, eps)
 
 
+# "library": torch's scaled_dot_product_attention; "native": this package's tcgen05 kernel
+ATTENTION_BACKEND = "library"
+
+
+def attention_native(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                     amax: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The package's own attention kernel (head dimension 128): ``[Lq, H, D]`` x ``[Lk, H, D]`` ->
+    ``[Lq, H, D]`` bf16, non-causal, scale 1/sqrt(D); q, k, v may be strided views (last
+    dimension contiguous).  ``amax``: a zeroed one-element fp32 tensor that receives max|o|."""
+    Lq, H, D = q.shape
+    Lk = k.shape[0]
+    for t in (q, k, v):
+        if t.dtype != torch.bfloat16 or t.stride(2) != 1 or t.shape[1:] != (H, D):
+            raise ValueError("attention_native wants bf16 [L, H, D] tensors with a contiguous last dimension")
+    if out is None:
+        out = torch.empty(Lq, H, D, dtype=torch.bfloat16, device=q.device)
+    N.check(N.lib.nvfp4_attention_bf16(
+        q.data_ptr(), q.stride(0), q.stride(1), k.data_ptr(), k.stride(0), k.stride(1),
+        v.data_ptr(), v.stride(0), v.stride(1), Lq, Lk, H, D, 1.0 / D ** 0.5, out.data_ptr(),
+        out.stride(0), out.stride(1), None if amax is None else amax.data_ptr(),
+        N.ptr(N.status_word(q.device)), N.stream_ptr()), "attention")
+    return out
+
+
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
     """``[Lq, H, D]`` x ``[Lk, H, D]`` -> ``[Lq, H, D]``, bf16, non-causal, scale 1/sqrt(D)."""
+    if ATTENTION_BACKEND == "native":
+        return attention_native(q, k, v)
     o = F.scaled_dot_product_attention(q.transpose(0, 1).unsqueeze(0), k.transpose(0, 1).unsqueeze(0),
                                        v.transpose(0, 1).unsqueeze(0))
     return o.squeeze(0).transpose(0, 1)

@@ -5,6 +5,7 @@
     python -m blackwell_diffusion_rtx6000_5090_i2v_b200.profile_case norm --m 27280 --k 3072
     python -m blackwell_diffusion_rtx6000_5090_i2v_b200.profile_case rope --m 27280 --k 3072
     python -m blackwell_diffusion_rtx6000_5090_i2v_b200.profile_case return --m 32760 --k 5120
+    python -m blackwell_diffusion_rtx6000_5090_i2v_b200.profile_case attention --m 27280 --k 3072
 
 Each case holds well under a few GB on the device, launches the kernel
 ``--iters`` times after ``--warmup`` launches, and prints the CUDA-event time.
@@ -35,7 +36,7 @@ def _time(fn, warmup, iters):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "quantize", "amax", "norm", "rope", "return"])
+    ap.add_argument("kernel", choices=["gemm", "quantize", "amax", "norm", "rope", "return", "attention"])
     ap.add_argument("--tiling", choices=["auto", "uniform", "alternating"], default="auto")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=9216)
@@ -44,6 +45,7 @@ def main():
     ap.add_argument("--bias", action="store_true")
     ap.add_argument("--gate", action="store_true", help="per-column fp32 gate in the epilogue")
     ap.add_argument("--residual", action="store_true", help="+ C (bf16 [m, n]) in the epilogue")
+    ap.add_argument("--library", action="store_true", help="attention: time the library kernel instead")
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--iters", type=int, default=3)
     a = ap.parse_args()
@@ -78,6 +80,22 @@ def main():
         N.check_status()
         nbytes = 2 * (2.0 + 2.0) * a.m * a.k          # q and k, read + written
         print(f"qk_norm_rope [{a.m}, 3x{a.k}]: {ms:.4f} ms, {nbytes / ms / 1e6:.1f} GB/s")
+    elif a.kernel == "attention":
+        # self-attention over m tokens, k/128 heads of 128, q/k/v as the column blocks of one
+        # [m, 3k] projection output
+        from . import dit
+        heads = a.k // 128
+        qkv = student_t_bf16((a.m, 3 * a.k), 13, device="cuda")
+        q, k, v = (t.view(a.m, heads, 128) for t in qkv.split(a.k, dim=-1))
+        out = torch.empty(a.m, heads, 128, dtype=torch.bfloat16, device="cuda")
+        amax = torch.zeros(1, device="cuda")
+        dit.ATTENTION_BACKEND = "library"
+        fn = (lambda: dit.attention(q, k, v)) if a.library else \
+            (lambda: dit.attention_native(q, k, v, amax=amax, out=out))
+        ms = _time(fn, a.warmup, a.iters)
+        N.check_status()
+        print(f"attention [{a.m}, {heads}, 128] ({'library' if a.library else 'native'}): {ms:.4f} ms, "
+              f"{4.0 * a.m * a.m * a.k / ms / 1e9:.1f} TFLOP/s")
     elif a.kernel == "return":
         # the attention-output return exchange on one GPU (one rank: every store is local), then
         # the flag wait that also reduces the amax: [m, k/128 heads, 128] -> the same buffer layout

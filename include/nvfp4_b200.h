@@ -244,6 +244,25 @@ NVFP4_API int nvfp4_attn_return_exchange_bf16(const void* o_bf16, int64_t o_row_
                                               void* const* rank_buffers, void* const* sync_blocks,
                                               int world, int rank, void* stream);
 
+/* Non-causal bf16 attention, head_dim == 128: o = softmax(q k^T * softmax_scale) v per head, on
+ * the tensor cores of sm_100a (tcgen05, accumulators and the probabilities in tensor memory,
+ * operands by TMA).  q is bf16 [q_len, heads, 128], k and v are bf16 [kv_len, heads, 128], o is
+ * bf16 [q_len, heads, 128]; every tensor is addressed by a token stride and a head stride in
+ * elements (multiples of 8), so the column blocks of a fused QKV projection can be passed
+ * without a copy.  amax_dev (nullable) receives max|o| by an atomic maximum on the float's bit
+ * pattern: zero it before the call and hand it to nvfp4_quantize_bf16 afterwards -- the
+ * quantizer of the attention-out linear then needs no amax pass.  status_dev (nullable) records
+ * 0xA00 + a code if a device-side wait gives up.  Replaces flash_attn_qkvpacked_func at
+ * fx/src/s4/models/wan22/wan_transformer_fast.py:47-58 and F.scaled_dot_product_attention at
+ * fx/src/s4/models/wan22/wan_transformer.py:126-129,164-167. */
+NVFP4_API int nvfp4_attention_bf16(const void* q_bf16, int64_t q_row_stride, int64_t q_head_stride,
+                                   const void* k_bf16, int64_t k_row_stride, int64_t k_head_stride,
+                                   const void* v_bf16, int64_t v_row_stride, int64_t v_head_stride,
+                                   int64_t q_len, int64_t kv_len, int heads, int head_dim,
+                                   float softmax_scale, void* o_bf16, int64_t o_row_stride,
+                                   int64_t o_head_stride, float* amax_dev, int* status_dev,
+                                   void* stream);
+
 /* Has no counterpart in the reference.  One whole linear, y = act(x W^T + bias), for
  * callers that cannot allocate device memory (code inside a region where cudaMalloc is not
  * allowed, fixed-budget real-time loops, plug-ins handed only input and output pointers):
