@@ -7,8 +7,9 @@
 // One CTA owns 256 query rows of one head as two 128-row tiles, and walks the keys 128 at a
 // time.  Per key tile and query tile:
 //     S = Q K^T           tcgen05.mma, both operands from shared memory, S in tensor memory
-//     P = exp2(S*c - m)   one thread per query row: tcgen05.ld, row max, exp2, row sum,
-//                         bf16 P written back over S with tcgen05.st
+//     P = exp2(S*c - m)   two threads per query row (64 keys each): tcgen05.ld, row max (the
+//                         halves meet through shared memory), exp2, row sum, bf16 P written
+//                         back over S with tcgen05.st
 //     O += P V            tcgen05.mma with P read from tensor memory and V (keys x d, d
 //                         contiguous: an MN-major operand) from shared memory
 // The two query tiles alternate on the tensor pipe: while the threads of one tile run the
@@ -21,7 +22,12 @@
 // Shared memory: Q0, Q1 (32 KiB each), a ring of four 32 KiB K/V tiles (K0 V0 K1 V1 ...),
 // every tile as two 128-row x 128-byte halves in the 128-byte swizzle that TMA writes.
 //
-// Warps 0-3: softmax + epilogue of query tile 0; 4-7: of tile 1; 8: TMA loads; 9: MMA issue.
+// Warps 0-7: softmax + epilogue of query tile 0 (warp & 3 = the 32-lane quarter of tensor memory
+// it may touch, bit 2 = which 64 keys); 8-15: of tile 1; 16: TMA loads; 17: MMA issue; 18-19
+// idle (they complete the fifth warpgroup, which hands its registers to the softmax warps).
+// Two warps per scheduler and tile matter: one warp alone issues in order and leaves the FMA,
+// ALU and special-function pipes waiting on each other (measured: 1730 cycles per tile with
+// four warps per tile against a tensor-pipe budget of 1024).
 // Every wait is bounded: when one runs out the kernel records where in *status, raises a
 // CTA-wide flag so that every role leaves its loop, and releases its tensor memory.
 #include <cuda.h>
@@ -42,11 +48,21 @@ constexpr int kHalfBytes = 128 * 128;     // 128 rows x 64 bf16
 constexpr int kTileBytes = 2 * kHalfBytes;
 constexpr int kKvSlots = 4;
 constexpr int kDataBytes = (kQTiles + kKvSlots) * kTileBytes;
-constexpr int kSmemBytes = kDataBytes + 1024 /*align slack*/ + 256 /*barriers*/;
-constexpr int kThreads = 320;
+constexpr int kSmemBytes = kDataBytes + 1024 /*align slack*/ + 256 /*barriers*/ + 4096 /*row exchange*/;
+constexpr int kSoftmaxWarps = 16;         // eight per query tile
+constexpr int kLoaderWarp = 16, kIssuerWarp = 17;
+constexpr int kThreads = 640;             // five warpgroups
+constexpr int kRegsSoftmax = 104, kRegsHelper = 56;
+constexpr int kXchgBytes = kQTiles * 2 * 2 * kBQ * 4;   // [tile][parity][half][row] floats
 constexpr int kTmemCols = 512;
 constexpr int kColS = 0, kColO = 256;     // + 128 * tile
 constexpr float kRescaleStep = 8.f;       // raise the running maximum only past 2^8
+#ifndef NVFP4_ATTN_FMA_EXP_EVERY
+#define NVFP4_ATTN_FMA_EXP_EVERY 4
+#endif
+// Every kFmaExpEvery-th element pair takes 2^x on the FMA pipe (0: none), spread evenly so that
+// the special-function unit works through its pairs while the FMA pipe works through these.
+constexpr int kFmaExpEvery = NVFP4_ATTN_FMA_EXP_EVERY;
 constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 2 GHz
 constexpr int kErrBase = 0xA00;
 
@@ -202,6 +218,31 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+// 2^x for a pair, x <= 8, on the FMA pipe instead of the special-function unit (which is the
+// scarcer resource here: 16 results per clock per SM against 128 FMA lanes).  x = i + f with
+// f in [-0.5, 0.5] by magic-number rounding, a cubic for 2^f (relative error 7.5e-5, a fiftieth
+// of a bf16 rounding step), and i added into the exponent field.  x is clamped at -126, where
+// the result (1e-38) is already nothing next to the row's largest term.
+__device__ __forceinline__ float2 exp2_fma(float2 x) {
+  const float kMagic = 12582912.f;   // 1.5 * 2^23: the sum's low mantissa bits hold round(x)
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const float2 magic = make_float2(kMagic, kMagic);
+  const float2 r = f2_add(x, magic);
+  const float2 f = f2_sub(x, f2_sub(r, magic));
+  float2 y = f2_fma(f, make_float2(0.0551716685f, 0.0551716685f), make_float2(0.242611125f, 0.242611125f));
+  y = f2_fma(y, f, make_float2(0.693260968f, 0.693260968f));
+  y = f2_fma(y, f, make_float2(0.999928057f, 0.999928057f));
+  y.x = __int_as_float(__float_as_int(y.x) + (__float_as_int(r.x) << 23));
+  y.y = __int_as_float(__float_as_int(y.y) + (__float_as_int(r.y) << 23));
+  return y;
+}
+
 // Shared-memory matrix descriptors, 128-byte swizzle (layout code 2, descriptor version 1).
 // K-major operand (Q, K: rows of 64 contraction elements = 128 bytes): 8-row groups 1024 bytes
 // apart (stride offset); the leading offset is unused.
@@ -244,6 +285,8 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   auto p_full = [&](int t) { return bar_base + 8u * (3 + 2 * kKvSlots + t); };
   auto o_full = [&](int t) { return bar_base + 8u * (5 + 2 * kKvSlots + t); };
   static_assert(8 * (7 + 2 * kKvSlots) <= 248, "barriers overrun their area");
+  float* xchg = reinterpret_cast<float*>(smem_gen + kDataBytes + 256);
+  static_assert(kXchgBytes <= 4096, "row exchange overruns its area");
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -259,14 +302,14 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
     for (int t = 0; t < kQTiles; ++t) {
       mbar_init(s_full(t), 1);
-      mbar_init(p_full(t), kBQ);     // every softmax thread of the tile arrives
+      mbar_init(p_full(t), 2 * kBQ);     // every softmax thread of the tile arrives
       mbar_init(o_full(t), 1);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (warp == 9) {
+  if (warp == kIssuerWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                  ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols)
                  : "memory");
@@ -277,7 +320,10 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 8) {
+  if (warp >= kSoftmaxWarps) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsHelper));
+  }
+  if (warp == kLoaderWarp) {
     // ----------------------------------------------------------- loader ----
     const uint32_t on = elect_one();
     bool ok = true;
@@ -305,7 +351,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       while (clock64() - t0 < 2000000LL) {
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == kIssuerWarp) {
     // ------------------------------------------------------- MMA issuer ----
     const uint32_t on = elect_one();
     const uint32_t idesc_s = make_idesc(false);
@@ -360,14 +406,20 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       tc_commit(kv_empty(sv), on);
       if (has_next) tc_commit(kv_empty(sk), on);
     }
-  } else {
+  } else if (warp < kSoftmaxWarps) {
     // ----------------------------------------------- softmax + epilogue ----
-    const int t = warp >> 2;
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
+    const int t = warp >> 3;
+    const int half = (warp >> 2) & 1;          // which 64 keys of the tile / 64 columns of O
     const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;         // row in the tile
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    const uint32_t s_addr = tmem_base + lane_addr + kColS + t * 128;
-    const uint32_t o_addr = tmem_base + lane_addr + kColO + t * 128;
-    const int64_t row = q0 + t * kBQ + quarter * 32 + lane;
+    const uint32_t s_addr = tmem_base + lane_addr + kColS + t * 128 + half * 64;
+    const uint32_t p_addr = tmem_base + lane_addr + kColS + t * 128 + half * 32;
+    const uint32_t o_addr = tmem_base + lane_addr + kColO + t * 128 + half * 64;
+    const int64_t row = q0 + t * kBQ + r;
+    const int pair_bar = 1 + t * 4 + quarter;  // named barrier of the two warps that share these rows
+    auto xslot = [&](int parity, int h) { return xchg + ((t * 2 + parity) * 2 + h) * kBQ + r; };
     const float c = p.scale_log2;
     float m_ref = 0.f, l = 0.f;
     bool ok = true;
@@ -376,31 +428,37 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      uint32_t s[128];
+      uint32_t s[64];
       tc_ld32(s_addr, s);
       tc_ld32(s_addr + 32, s + 32);
-      tc_ld32(s_addr + 64, s + 64);
-      tc_ld32(s_addr + 96, s + 96);
       tc_wait_ld();
       if (j == n - 1) {
         // keys past the end of the sequence (their K rows were read as zeros) get no weight
-        const int valid = (int)(p.kv_len - (int64_t)j * kBKV);
-        if (valid < kBKV) {
+        const int valid = (int)(p.kv_len - (int64_t)j * kBKV) - half * 64;
+        if (valid < 64) {
 #pragma unroll
-          for (int e = 0; e < 128; ++e)
+          for (int e = 0; e < 64; ++e)
             if (e >= valid) s[e] = 0xFF800000u;   // -inf
         }
       }
-      float mx0 = __uint_as_float(s[0]), mx1 = __uint_as_float(s[1]);
-      float mx2 = __uint_as_float(s[2]), mx3 = __uint_as_float(s[3]);
+      float mx0 = max3(__uint_as_float(s[0]), __uint_as_float(s[1]), __uint_as_float(s[2]));
+      float mx1 = max3(__uint_as_float(s[3]), __uint_as_float(s[4]), __uint_as_float(s[5]));
+      float mx2 = fmaxf(__uint_as_float(s[6]), __uint_as_float(s[7]));
+      float mx3 = -INFINITY;
 #pragma unroll
-      for (int e = 4; e < 128; e += 4) {
-        mx0 = fmaxf(mx0, __uint_as_float(s[e]));
-        mx1 = fmaxf(mx1, __uint_as_float(s[e + 1]));
-        mx2 = fmaxf(mx2, __uint_as_float(s[e + 2]));
-        mx3 = fmaxf(mx3, __uint_as_float(s[e + 3]));
+      for (int e = 8; e < 64; e += 8) {
+        mx0 = max3(mx0, __uint_as_float(s[e]), __uint_as_float(s[e + 1]));
+        mx1 = max3(mx1, __uint_as_float(s[e + 2]), __uint_as_float(s[e + 3]));
+        mx2 = max3(mx2, __uint_as_float(s[e + 4]), __uint_as_float(s[e + 5]));
+        mx3 = max3(mx3, __uint_as_float(s[e + 6]), __uint_as_float(s[e + 7]));
       }
-      const float mc = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * c;
+      // the two halves of a row meet: after this barrier both warps that own these 32 rows have
+      // finished reading S, so the probabilities may go over it
+      float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      *xslot(j & 1, half) = mx;
+      asm volatile("bar.sync %0, %1;" ::"r"(pair_bar), "n"(64) : "memory");
+      mx = fmaxf(mx, *xslot(j & 1, half ^ 1));
+      const float mc = mx * c;
       if (j == 0) {
         m_ref = mc;
       } else {
@@ -410,9 +468,8 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           const float alpha = raise ? ex2(m_ref - mc) : 1.f;
           if (raise) m_ref = mc;
           l *= alpha;
-          // (rare: eight columns at a time keeps it out of the way of the 128 live S values)
 #pragma unroll 1
-          for (int g = 0; g < kD / 8; ++g) {
+          for (int g = 0; g < 64 / 8; ++g) {
             uint32_t o[8];
             tc_ld8(o_addr + g * 8, o);
             tc_wait_ld();
@@ -422,21 +479,40 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
           }
         }
       }
-      // p = exp2(s*c - m): two per FMA; the row sum in fp32 before the rounding to bf16
+      // p = exp2(s*c - m); the row sum in fp32 before the rounding to bf16; bf16 pairs go back
+      // over S (32 packed columns per thread)
       const float2 c2 = make_float2(c, c);
       const float2 nm2 = make_float2(-m_ref, -m_ref);
-      float2 sum = make_float2(0.f, 0.f);
+      float2 sum0 = make_float2(0.f, 0.f), sum1 = make_float2(0.f, 0.f);
+      // three sweeps rather than one loop, so that consecutive exponentials do not depend on one
+      // another's results: the special-function unit takes one warp instruction every 8 cycles
+      // and a sum or a pack right behind each would stall on it
 #pragma unroll
-      for (int e = 0; e < 64; ++e) {
-        float2 x = f2_fma(make_float2(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1])), c2, nm2);
-        x.x = ex2(x.x);
-        x.y = ex2(x.y);
-        sum = f2_add(sum, x);
-        s[e] = f2_to_bf16x2(x);      // s[e] is dead once e >= its own index: 2e, 2e+1 >= e
+      for (int e = 0; e < 32; ++e) {
+        const float2 x = f2_fma(make_float2(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1])), c2, nm2);
+        s[2 * e] = __float_as_uint(x.x);
+        s[2 * e + 1] = __float_as_uint(x.y);
       }
-      l += sum.x + sum.y;
-      tc_st32(s_addr, s);
-      tc_st32(s_addr + 32, s + 32);
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        float2 x = make_float2(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1]));
+        if (kFmaExpEvery > 0 && e % (kFmaExpEvery > 0 ? kFmaExpEvery : 1) == 0) {
+          x = exp2_fma(x);
+        } else {
+          x.x = ex2(x.x);
+          x.y = ex2(x.y);
+        }
+        s[2 * e] = __float_as_uint(x.x);
+        s[2 * e + 1] = __float_as_uint(x.y);
+      }
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        const float2 x = make_float2(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1]));
+        if (e & 1) sum1 = f2_add(sum1, x); else sum0 = f2_add(sum0, x);
+        s[e] = f2_to_bf16x2(x);      // s[e] is dead by now: 2e, 2e+1 >= e
+      }
+      l += (sum0.x + sum0.y) + (sum1.x + sum1.y);
+      tc_st32(p_addr, s);
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(p_full(t));
@@ -447,12 +523,16 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     }
     if (ok) {
       tc_fence_after();
+      // the row sum of both halves (the slots of parity n & 1 were last used two tiles ago)
+      *xslot(n & 1, half) = l;
+      asm volatile("bar.sync %0, %1;" ::"r"(pair_bar), "n"(64) : "memory");
+      l += *xslot(n & 1, half ^ 1);
       const float inv = 1.f / l;
       const bool live = row < p.q_len;
-      uint8_t* dst = p.o + (live ? row : 0) * p.o_row_bytes + (int64_t)head * p.o_head_bytes;
+      uint8_t* dst = p.o + (live ? row : 0) * p.o_row_bytes + (int64_t)head * p.o_head_bytes + half * 128;
       uint32_t amax2 = 0u;
 #pragma unroll
-      for (int g = 0; g < 4; ++g) {
+      for (int g = 0; g < 2; ++g) {
         uint32_t o[32];
         tc_ld32(o_addr + g * 32, o);
         tc_wait_ld();
@@ -478,7 +558,7 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == kIssuerWarp) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "r"(kTmemCols)

@@ -422,12 +422,19 @@ class WanBlock:
             _mark("qk_norm_rope")
             q, k, v = ulysses.all_to_all_packed(send, group).split(cfg.head_dim, dim=-1)
             _mark("exchange")
-        o = attention(q, k, v)
+        amax = None
+        if ATTENTION_BACKEND == "native" and group is None:
+            # the kernel folds max|o| into its epilogue: the quantizer in front of the
+            # attention-out linear gets its amax from here
+            amax = self._amax.zero_()
+            o = attention_native(q, k, v, amax=amax)
+        else:
+            o = attention(q, k, v)
         _mark("self_attention")
         if group is not None:
             o = ulysses.heads_to_seq(o.contiguous(), group)
             _mark("exchange")
-        return o.reshape(L, cfg.dim), None
+        return o.reshape(L, cfg.dim), amax
 
     def _self_attention(self, q, k, v, cos, sin, group):
         cfg = self.cfg

@@ -38,6 +38,8 @@ def main(argv=None) -> int:
     ap.add_argument("--warmup", type=int, default=1)
     ap.add_argument("--check", action="store_true", help="cosine against the dequant model")
     ap.add_argument("--sdpa", choices=["default", "flash", "cudnn"], default="default")
+    ap.add_argument("--attention", choices=["library", "native"], default="library",
+                    help="library: torch's scaled_dot_product_attention; native: the package's tcgen05 kernel")
     ap.add_argument("--graph", action="store_true",
                     help="single GPU: also time the step replayed from a CUDA graph")
     ap.add_argument("--exchange", choices=["nccl", "peer"], default="nccl",
@@ -67,6 +69,7 @@ def main(argv=None) -> int:
     text = torch.randn(512, cfg.text_dim, generator=g, device="cuda").to(torch.bfloat16)
     tokens = Fr * (H // 2) * (W // 2)
 
+    dit.ATTENTION_BACKEND = args.attention
     backends = None
     if args.sdpa != "default":
         from torch.nn.attention import SDPBackend
@@ -200,6 +203,7 @@ def main(argv=None) -> int:
             "config": {"workload": f"wan2.2 {args.config} shape, {len(model.blocks)} blocks, "
                                    f"{tokens} tokens, text 512x{cfg.text_dim}",
                        "tokens_per_rank": tokens // world, "sdpa": args.sdpa,
+                       "attention": args.attention,
                        "exchange": args.exchange if world > 1 else None,
                        "amax_sync": bool(args.amax_sync and world > 1),
                        "parallelism": f"ulysses{world}" if world > 1 else "single"},

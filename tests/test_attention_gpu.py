@@ -109,3 +109,27 @@ def test_attention_rejects_bad_arguments():
     assert call(scale=0.0) == 1
     assert call(qs=132) == 2           # token stride not a multiple of 16 bytes
     torch.cuda.synchronize()
+
+
+def test_block_with_native_attention_matches_library():
+    """A DiT block stack with the package's attention kernel (self-attention hands its folded
+    max|o| to the attention-out quantizer, cross-attention runs through it too) against the
+    same model on the library kernel: the two attention kernels differ by bf16 roundings only."""
+    from blackwell_diffusion_rtx6000_5090_i2v_b200 import dit, nvfp4
+    cfg = dit.WanDiTConfig(dim=512, heads=4, ffn=1024, layers=2, in_channels=16, out_channels=16,
+                           text_dim=256)
+    model = dit.WanDiT(cfg, device="cuda", seed=11)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    latent = torch.randn(16, 4, 16, 20, generator=g, device="cuda").to(torch.bfloat16)   # 320 tokens
+    text = torch.randn(24, 256, generator=g, device="cuda").to(torch.bfloat16)
+    old = dit.ATTENTION_BACKEND
+    try:
+        dit.ATTENTION_BACKEND = "library"
+        a = model.forward(latent, 500.0, text)
+        dit.ATTENTION_BACKEND = "native"
+        b = model.forward(latent, 500.0, text)
+    finally:
+        dit.ATTENTION_BACKEND = old
+    nvfp4.check_status()
+    cos = torch.nn.functional.cosine_similarity(a.flatten().double(), b.flatten().double(), dim=0).item()
+    assert cos >= 0.999, cos
