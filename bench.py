@@ -316,6 +316,51 @@ def dit_step_report(world: int, rank: int, local_rank: int, steps: int = 3):
 
 # ------------------------------------------------------------------ GPU arm --
 
+def attention_report():
+    """The package's tcgen05 attention kernel beside the library kernel on the Wan 2.2 5B
+    self-attention shape (27280 tokens, 24 heads of 128): burst timing, 5 launches each."""
+    import torch
+    from blackwell_diffusion_rtx6000_5090_i2v_b200 import dit
+    from blackwell_diffusion_rtx6000_5090_i2v_b200.synthetic import student_t_bf16
+    L, H = 27280, 24
+    qkv = student_t_bf16((L, 3 * H * 128), 13, device="cuda")
+    q, k, v = (t.view(L, H, 128) for t in qkv.split(H * 128, dim=-1))
+    out = torch.empty(L, H, 128, dtype=torch.bfloat16, device="cuda")
+    amax = torch.zeros(1, device="cuda")
+    old = dit.ATTENTION_BACKEND
+    dit.ATTENTION_BACKEND = "library"
+
+    def timed(fn, n=5):
+        for _ in range(3):
+            r = fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            r = fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n, r
+
+    try:
+        ms_lib, o_lib = timed(lambda: dit.attention(q, k, v))
+        ms_own, o_own = timed(lambda: dit.attention_native(q, k, v, amax=amax.zero_(), out=out))
+    finally:
+        dit.ATTENTION_BACKEND = old
+    flops = 4.0 * L * L * H * 128
+    peaks = measured_peaks()
+    own, lib = flops / ms_own / 1e9, flops / ms_lib / 1e9
+    return {"kernel": "attention_kernel (tcgen05, bf16, max|o| folded in)", "bound": "tensor",
+            "workload": f"[{L}, {H}, 128] self-attention, non-causal, q/k/v as column blocks of one "
+                        "[L, 3*H*128] tensor",
+            "achieved": own, "unit": "TFLOP/s", "ms": ms_own, "peak": peaks["bf16_tflops"],
+            "frac": own / peaks["bf16_tflops"], "peak_source": f"{peaks['source']} cuBLAS bf16 burst",
+            "library": {"kernel": "F.scaled_dot_product_attention", "achieved": lib, "ms": ms_lib},
+            "frac_of_library": own / lib,
+            "max_abs_diff_vs_library": float((o_own.float() - o_lib.float()).abs().max()),
+            "amax_matches_output": float(amax) == float(o_own.float().abs().max())}
+
+
 def run_ours(args, rank: int, local_rank: int, world: int):
     import torch
     import torch.distributed as dist
@@ -558,6 +603,13 @@ def run_ours(args, rank: int, local_rank: int, world: int):
     qa_shape = (qa.m, qa.k)
     del staged, host_in, host_out, runner, inputs, gemm_events, sus_events, late, big, xin, qa, qn
     torch.cuda.empty_cache()
+    attention = None
+    if rank == 0 and not args.skip_dit:
+        try:
+            attention = attention_report()
+        except Exception as e:
+            attention = {"failed": f"{type(e).__name__}: {str(e)[:300]}"}
+        torch.cuda.empty_cache()
     dit_step = None
     if not args.skip_dit:
         try:
@@ -643,6 +695,7 @@ def run_ours(args, rank: int, local_rank: int, world: int):
                              "scale with N",
                     "cpu_binding": numa},
             "clocks": clocks.summary(),
+            "attention": attention,
             "dit_step": dit_step,
         }
         if world == 1 and not args.skip_cpu:
