@@ -318,7 +318,7 @@ def dit_step_report(world: int, rank: int, local_rank: int, steps: int = 3):
 
 def attention_report():
     """The package's tcgen05 attention kernel beside the library kernel on the Wan 2.2 5B
-    self-attention shape (27280 tokens, 24 heads of 128): burst timing, 5 launches each."""
+    self-attention shape (27280 tokens, 24 heads of 128): four alternating rounds of three launches."""
     import torch
     from blackwell_diffusion_rtx6000_5090_i2v_b200 import dit
     from blackwell_diffusion_rtx6000_5090_i2v_b200.synthetic import student_t_bf16
@@ -330,9 +330,8 @@ def attention_report():
     old = dit.ATTENTION_BACKEND
     dit.ATTENTION_BACKEND = "library"
 
-    def timed(fn, n=5):
-        for _ in range(3):
-            r = fn()
+    def timed(fn, n=3):
+        r = fn()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -342,11 +341,18 @@ def attention_report():
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / n, r
 
+    # the two kernels take turns, so that neither is always the one measured on the warmer GPU;
+    # the best round of each is reported, all rounds are listed
+    own_ms, lib_ms = [], []
     try:
-        ms_lib, o_lib = timed(lambda: dit.attention(q, k, v))
-        ms_own, o_own = timed(lambda: dit.attention_native(q, k, v, amax=amax.zero_(), out=out))
+        for _ in range(4):
+            ms, o_own = timed(lambda: dit.attention_native(q, k, v, amax=amax.zero_(), out=out))
+            own_ms.append(ms)
+            ms, o_lib = timed(lambda: dit.attention(q, k, v))
+            lib_ms.append(ms)
     finally:
         dit.ATTENTION_BACKEND = old
+    ms_own, ms_lib = min(own_ms), min(lib_ms)
     flops = 4.0 * L * L * H * 128
     peaks = measured_peaks()
     own, lib = flops / ms_own / 1e9, flops / ms_lib / 1e9
@@ -357,6 +363,7 @@ def attention_report():
             "frac": own / peaks["bf16_tflops"], "peak_source": f"{peaks['source']} cuBLAS bf16 burst",
             "library": {"kernel": "F.scaled_dot_product_attention", "achieved": lib, "ms": ms_lib},
             "frac_of_library": own / lib,
+            "rounds_ms": {"own": [round(t, 3) for t in own_ms], "library": [round(t, 3) for t in lib_ms]},
             "max_abs_diff_vs_library": float((o_own.float() - o_lib.float()).abs().max()),
             "amax_matches_output": float(amax) == float(o_own.float().abs().max())}
 
