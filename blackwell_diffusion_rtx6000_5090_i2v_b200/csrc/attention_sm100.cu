@@ -426,7 +426,14 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     for (int j = 0; j < n; ++j) {
       ok = mbar_wait(s_full(t), (uint32_t)j & 1u, abort_flag, p.status, kErrBase + 0x40 + t);
       ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      if (!ok) {
+        // The partner warp may have seen this barrier flip a moment before the abort flag went
+        // up and be on its way to this key tile's meeting point, which has no time limit of its
+        // own: arrive there without waiting, so that it gets through.  It cannot reach the next
+        // meeting point: the next S needs this warp's probabilities, which never come.
+        asm volatile("bar.arrive %0, %1;" ::"r"(pair_bar), "n"(64) : "memory");
+        break;
+      }
       tc_fence_after();
       uint32_t s[64];
       tc_ld32(s_addr, s);
@@ -520,6 +527,8 @@ attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     if (ok) {
       ok = mbar_wait(o_full(t), 0, abort_flag, p.status, kErrBase + 0x60 + t);
       ok = __all_sync(0xffffffffu, ok);
+      // as above: the partner may be on its way to the meeting point of the row sums
+      if (!ok) asm volatile("bar.arrive %0, %1;" ::"r"(pair_bar), "n"(64) : "memory");
     }
     if (ok) {
       tc_fence_after();
