@@ -658,7 +658,24 @@ class WanDiT:
     def forward(self, latent: torch.Tensor, t: float, text: torch.Tensor, mode: str = "nvfp4",
                 group: Optional[dist.ProcessGroup] = None, exchange: str = "nccl",
                 amax_sync: bool = False) -> torch.Tensor:
-        """latent ``[C, F, H, W]`` bf16, text ``[512, 4096]`` bf16 -> ``[C_out, F, H, W]``.
+        y, grid = self.forward_tokens(latent, t, text, mode, group, exchange, amax_sync)
+        return self.gather_tokens(y, grid, group)
+
+    def gather_tokens(self, y: torch.Tensor, grid, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+        """The ranks' token shards of the head's output -> the full ``[C_out, F, H, W]`` on every
+        rank (one all-gather; nothing to do on a single GPU)."""
+        if group is not None and dist.get_world_size(group) > 1:
+            parts = [torch.empty_like(y) for _ in range(dist.get_world_size(group))]
+            dist.all_gather(parts, y.contiguous(), group=group)
+            y = torch.cat(parts, dim=0)
+        return self._unpatchify(y, grid)
+
+    def forward_tokens(self, latent: torch.Tensor, t: float, text: torch.Tensor, mode: str = "nvfp4",
+                       group: Optional[dist.ProcessGroup] = None, exchange: str = "nccl",
+                       amax_sync: bool = False):
+        """The step up to and including the output head: ``(this rank's rows of the head's output,
+        token grid)``; ``gather_tokens`` finishes it.
+        latent ``[C, F, H, W]`` bf16, text ``[512, 4096]`` bf16 -> ``[C_out, F, H, W]``.
         With ``group`` each rank processes its contiguous shard of the token sequence and
         returns the full output (gathered) on every rank.  ``exchange``: ``"nccl"`` (two
         all-to-alls per block) or ``"peer"`` (stores into peer memory fused into the q/k norm +
@@ -693,28 +710,39 @@ class WanDiT:
         for i, blk in enumerate(self.blocks):
             x = blk.forward(x, ctx, temb6, cos, sin, mode, group if P > 1 else None, cos_sin, px,
                             kvs[i] if kvs is not None else None, hook, self._scratch)
-        y = self._head(x, temb, mode, hook)
-        if P > 1:
-            parts = [torch.empty_like(y) for _ in range(P)]
-            dist.all_gather(parts, y.contiguous(), group=group)
-            y = torch.cat(parts, dim=0)
-        return self._unpatchify(y, grid)
+        return self._head(x, temb, mode, hook), grid
 
-    def capture(self, latent: torch.Tensor, t: float, text: torch.Tensor):
-        """Record one single-GPU NVFP4 step into a CUDA graph (the static-shape capture of
+    def capture(self, latent: torch.Tensor, t: float, text: torch.Tensor,
+                group: Optional[dist.ProcessGroup] = None):
+        """Record one NVFP4 step into a CUDA graph (the static-shape capture of
         fx/src/s4/models/wan_22/wan_attention_static.py:566-630).  Returns ``(graph, out)``:
         ``graph.replay()`` re-runs the step on whatever ``latent`` and ``text`` then contain
         (same tensors, same timestep) and leaves the result in ``out``.  Everything the step
         launches is capturable: the library's kernels run on the current stream, never
-        synchronise with the host, and take their temporaries from the torch allocator."""
+        synchronise with the host, and take their temporaries from the torch allocator.
+
+        With ``group`` the sharded step with the peer-store exchange is recorded: its flag waits
+        keep their epochs in device memory, so every replay waits for the peers' matching replay
+        (all ranks must replay the same number of times).  ``out`` is then this rank's rows of the
+        head's output and ``(graph, out, grid)`` is returned; ``gather_tokens(out, grid, group)``
+        (an all-gather, outside the graph) completes the step."""
+        sharded = group is not None and dist.get_world_size(group) > 1
+        kw = dict(group=group, exchange="peer") if sharded else {}
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(side):
-            self.forward(latent, t, text)           # warm-up: tables, status word, lazy buffers
+            self.forward_tokens(latent, t, text, **kw)   # warm-up: tables, status word, lazy buffers
         torch.cuda.current_stream(self.device).wait_stream(side)
+        if sharded:
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group)                          # every rank's warm-up step has finished
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            out = self.forward(latent, t, text)
+            out, grid = self.forward_tokens(latent, t, text, **kw)
+            if not sharded:
+                out = self._unpatchify(out, grid)
+        if sharded:
+            return graph, out, grid
         return graph, out
 
     def compare_blocks(self, latent: torch.Tensor, t: float, text: torch.Tensor

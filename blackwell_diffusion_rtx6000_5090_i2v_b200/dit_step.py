@@ -41,7 +41,8 @@ def main(argv=None) -> int:
     ap.add_argument("--attention", choices=["library", "native"], default="library",
                     help="library: torch's scaled_dot_product_attention; native: the package's tcgen05 kernel")
     ap.add_argument("--graph", action="store_true",
-                    help="single GPU: also time the step replayed from a CUDA graph")
+                    help="also time the step replayed from a CUDA graph (single GPU, or sharded with "
+                         "--exchange peer)")
     ap.add_argument("--exchange", choices=["nccl", "peer"], default="nccl",
                     help="head/sequence exchange: all-to-alls, or stores into peer memory")
     ap.add_argument("--amax-sync", action="store_true",
@@ -113,19 +114,29 @@ def main(argv=None) -> int:
         dit.TIMELINE = None
 
         checks = {}
-        if args.graph and world == 1:
-            graph, gout = model.capture(latent, 500.0, text)
+        if args.graph and (world == 1 or args.exchange == "peer") and not args.amax_sync:
+            if world == 1:
+                graph, gout = model.capture(latent, 500.0, text)
+                finish = lambda: gout                                      # noqa: E731
+            else:
+                graph, gshard, ggrid = model.capture(latent, 500.0, text, group=group)
+                finish = lambda: model.gather_tokens(gshard, ggrid, group)  # noqa: E731
             gtimes = []
             for _ in range(args.steps):
                 fence()
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
                 graph.replay()
+                gy = finish()
                 e1.record()
                 fence()
-                gtimes.append(e0.elapsed_time(e1))
+                t = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+                if world > 1:
+                    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                gtimes.append(float(t))
+            nvfp4.check_status()
             checks["graph_replay_ms"] = round(statistics.median(gtimes), 3)
-            checks["graph_replay_equals_eager"] = bool(torch.equal(gout, y))
+            checks["graph_replay_equals_eager"] = bool(torch.equal(gy, y))
         if args.check:
             ref = step(mode="dequant")
             checks["cosine_vs_dequant_model"] = _cos(y, ref)

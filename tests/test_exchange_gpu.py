@@ -44,6 +44,16 @@ def _worker(rank, world, port, out):
         nvfp4.check_status()
         cos = torch.dot(d.double().flatten(), full.double().flatten()) / (d.double().norm() * full.double().norm())
         assert float(cos) >= 1 - 1e-9, float(cos)
+        # the sharded step recorded into a CUDA graph: the flag waits' epochs live in device
+        # memory, so each replay meets the peers' matching replay; same bits as the eager step
+        graph, shard, grid = model.capture(latent, 500.0, text, group=grp)
+        for _ in range(3):
+            graph.replay()
+            g = model.gather_tokens(shard, grid, grp)
+            nvfp4.check_status()
+            assert torch.equal(g, b)
+        # and eager steps still work after replays (the epochs moved on consistently)
+        assert torch.equal(model.forward(latent, 500.0, text, group=grp, exchange="peer"), b)
         out[rank] = 1
     finally:
         dist.destroy_process_group()
