@@ -68,6 +68,23 @@ def test_argument_validation_without_device():
                                           None, None, None, None, None) == 2
     assert L.nvfp4_norm_mod_quantize_bf16(fake + 8, 4, 64, None, None, None, None, fake, fake, fake,
                                           None, None, None, None, None) == 2   # x itself
+    # attention: head dimension, key count, scale, pointers, strides and alignment are all
+    # checked before the device is looked at
+
+    def attn(q=fake, hd=128, lq=256, lk=256, scale=0.1, qs=384, o=fake, heads=1):
+        return L.nvfp4_attention_bf16(q, qs, 128, fake, 384, 128, fake, 384, 128, lq, lk, heads, hd, scale,
+                                      o, 128, 128, None, None, None)
+    assert attn(hd=64) == 1
+    assert attn(lk=0) == 1
+    assert attn(lq=-1) == 1
+    assert attn(scale=0.0) == 1
+    assert attn(heads=0) == 1
+    assert attn(q=None) == 1
+    assert attn(o=None) == 1
+    assert attn(qs=64) == 1              # token stride shorter than a head
+    assert attn(qs=132) == 2             # token stride not a multiple of 16 bytes
+    assert attn(q=fake + 8) == 2
+    assert attn(lq=0) == 0               # no queries: a no-op
 
 
 def test_host_api_mirrors_reference_names():
