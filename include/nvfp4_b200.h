@@ -252,7 +252,7 @@ NVFP4_API int nvfp4_attn_return_exchange_bf16(const void* o_bf16, int64_t o_row_
  * without a copy.  amax_dev (nullable) receives max|o| by an atomic maximum on the float's bit
  * pattern: zero it before the call and hand it to nvfp4_quantize_bf16 afterwards -- the
  * quantizer of the attention-out linear then needs no amax pass.  status_dev (nullable) records
- * 0xA00 + a code if a device-side wait gives up.  Replaces flash_attn_qkvpacked_func at
+ * 0xA00 + a code if a device-side wait gives up.  q_len == 0 is a no-op; kv_len must be at least 1.  Replaces flash_attn_qkvpacked_func at
  * fx/src/s4/models/wan22/wan_transformer_fast.py:47-58 and F.scaled_dot_product_attention at
  * fx/src/s4/models/wan22/wan_transformer.py:126-129,164-167. */
 NVFP4_API int nvfp4_attention_bf16(const void* q_bf16, int64_t q_row_stride, int64_t q_head_stride,
